@@ -90,7 +90,7 @@ def pages_of_group(spec: PagedCacheSpec, num_blocks: int, block_size: int, max_n
 def group_names(specs: list[PagedCacheSpec], pages: list[int]) -> list[GroupSpec]:
     return [
         GroupSpec(
-            f"kv{i}:{s.kv_heads}x{s.head_dim}" + (f"+{s.v_dim}" if s.v_dim != s.head_dim else "")
+            f"kv{i}:{s.kv_heads}x{s.head_dim}" + (f"+{s.v_dim}" if s.v_dim not in (0, s.head_dim) else "") + ("=v" if s.v_dim == 0 else "")
             + (f":w{s.window}" if s.window else "") + (f":first{s.keep_first}" if s.window and s.keep_first else ""),
             s.window, count, keep_first=s.keep_first if s.window else 0,
         )
@@ -155,7 +155,11 @@ def allocate_cache(
     # Keys and values of a group lie in one array when their heads are equally wide; else in two.
     arrays, key_arrays, value_arrays = [], [], []
     for s, entries, count in zip(specs, owners, pages):
-        if s.v_dim == s.head_dim:
+        if s.v_dim == 0:  # the values are a part of the key rows: no value pages
+            keys = torch.zeros((len(entries), count + 1, s.kv_heads, block_size, s.head_dim), dtype=dtype, device=device)
+            arrays.append(keys)
+            key_arrays.append(keys), value_arrays.append(None)
+        elif s.v_dim == s.head_dim:
             both = torch.zeros((len(entries), 2, count + 1, s.kv_heads, block_size, s.head_dim), dtype=dtype, device=device)
             arrays.append(both)
             key_arrays.append(both[:, 0]), value_arrays.append(both[:, 1])
@@ -172,7 +176,8 @@ def allocate_cache(
             g = group_of[entry]
             owner = entry if cache_of is None else cache_of
             index = owners[g].index(owner)
-            view.group, view.k, view.v = g, key_arrays[g][index], value_arrays[g][index]
+            view.group, view.k = g, key_arrays[g][index]
+            view.v = None if value_arrays[g] is None else value_arrays[g][index]
             view.writes = cache_of is None
         if state is not None:
             slot_groups.append(SlotGroupSpec(f"state{entry}:{'x'.join(map(str, state.shape))}"))

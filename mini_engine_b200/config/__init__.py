@@ -1,5 +1,6 @@
 """Typed configuration: the model's own ``config.json`` keys and the engine's options."""
 
+from mini_engine_b200.config.bevadra import BevadraConfig
 from mini_engine_b200.config.engine_config import EngineConfig
 from mini_engine_b200.config.model_spec import LayerSpec, ModelSpec, OrderEntry, PartSpec
 from mini_engine_b200.config.molotar import MolotarConfig
@@ -15,6 +16,7 @@ from mini_engine_b200.config.registry import (
 
 __all__ = [
     "Architecture",
+    "BevadraConfig",
     "EngineConfig",
     "LayerSpec",
     "ModelSpec",

@@ -7,7 +7,11 @@
 // s = (q . k) * scale; the query at position p sees keys at positions <= p (and > p - window
 // when a window is given); out = softmax(s) V.  Options: value heads of their own width (`value_dim`); a
 // softmax with one more, silent participant of score zero that has no value (`sink`: p_j = exp(s_j) /
-// (1 + sum exp(s))); and a multiplier per (token, head) on the output (`gate`, float32 [tokens][heads]).
+// (1 + sum exp(s))), or of a learned score per head (`sink_values`: exp(sink_h) in place of the 1); a multiplier
+// on the output (`gate`, float32 [tokens][heads][gate_width] with gate_width 1, one per head, or value_dim, one per
+// element); a distance bias that is linear in the distance (`slopes`, one per head: s -= slope_h * (p - j), after
+// the scale); and values that are the first value_dim elements of the key rows (`value_stride`: elements between
+// two value rows; pass the key pages as value pages and head_dim as the stride).
 //
 // Keys are visited in tiles of 32 whose boundaries are multiples of 32 in *absolute position*
 // and are combined in ascending order, so the arithmetic of a query depends only on its own
@@ -26,11 +30,15 @@ struct AttnArgs {
     float scale;
     int tokens, heads, kv_heads, head_dim, page_size, table_width, window;
     int value_dim, sink;
-    const float* gate;  // [tokens][heads] or null
+    const float* gate;  // [tokens][heads][gate_width] or null
+    int gate_width, value_stride;
+    const float* slopes;       // [heads] or null
+    const float* sink_values;  // [heads] or null (with sink: the silent participant's score, zero when null)
 };
 
 constexpr int ATTN_WARPS = 4;
-constexpr int MAX_DIM_PER_LANE = 16;  // head_dim <= 512
+constexpr int MAX_DIM_PER_LANE = 16;  // value_dim <= 512
+constexpr int MAX_KEY_DIM = 2048;     // the query is staged in shared memory
 
 template <typename T>
 __global__ void __launch_bounds__(ATTN_WARPS * 32) paged_attention_generic_kernel(AttnArgs a) {
@@ -53,6 +61,8 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32) paged_attention_generic_kerne
     for (int i = lane; i < d; i += 32) q[i] = to_float(q_src[i]);
     __syncwarp();
 
+    const float slope = a.slopes ? a.slopes[head] : 0.0f;
+    const size_t v_stride = static_cast<size_t>(a.value_stride);
     const int lowest = a.window > 0 ? max(position - a.window + 1, 0) : 0;
     float running_max = -INFINITY, denom = 0.0f;
     float acc[MAX_DIM_PER_LANE];
@@ -74,6 +84,7 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32) paged_attention_generic_kerne
             float dot = 0.0f;
             for (int i = 0; i < d; ++i) dot = fmaf(q[i], to_float(k_row[i]), dot);
             score = dot * a.scale;
+            if (a.slopes) score -= slope * static_cast<float>(position - key);
         }
         const float new_max = fmaxf(running_max, warp_max(score));
         if (new_max == -INFINITY) continue;  // nothing visible yet (uniform across the warp)
@@ -87,7 +98,7 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32) paged_attention_generic_kerne
             const float pj = __shfl_sync(0xffffffffu, p, j);
             const long long bj = __shfl_sync(0xffffffffu, base, j);
             if (bj < 0) continue;  // uniform across the warp
-            const T* v_row = v_pages + bj * dv;
+            const T* v_row = v_pages + bj * v_stride;
 #pragma unroll
             for (int i = 0; i < MAX_DIM_PER_LANE; ++i) {
                 const int e = lane + 32 * i;
@@ -96,13 +107,18 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32) paged_attention_generic_kerne
         }
     }
     T* out = static_cast<T*>(a.out) + (static_cast<size_t>(token) * a.heads + head) * dv;
-    if (a.sink) denom += expf(-running_max);  // the silent participant: exp(0 - max)
+    if (a.sink) denom += expf((a.sink_values ? a.sink_values[head] : 0.0f) - running_max);  // the silent participant
     float inv = 1.0f / denom;
-    if (a.gate) inv *= a.gate[static_cast<size_t>(token) * a.heads + head];
+    const float* gate = a.gate ? a.gate + (static_cast<size_t>(token) * a.heads + head) * a.gate_width : nullptr;
+    if (gate && a.gate_width == 1) inv *= gate[0];
 #pragma unroll
     for (int i = 0; i < MAX_DIM_PER_LANE; ++i) {
         const int e = lane + 32 * i;
-        if (e < dv) out[e] = from_float<T>(acc[i] * inv);
+        if (e < dv) {
+            float y = acc[i] * inv;
+            if (gate && a.gate_width > 1) y *= gate[e];
+            out[e] = from_float<T>(y);
+        }
     }
 }
 
@@ -110,13 +126,17 @@ ME_EXPORT int me_paged_attention_generic(const void* q, const void* k_pages, con
                                          const int* block_table, const int* entry_of_token,
                                          const int* positions, void* out, int type, float scale, int tokens,
                                          int heads, int kv_heads, int head_dim, int page_size, int table_width,
-                                         int window, int value_dim, int sink, const float* gate,
+                                         int window, int value_dim, int sink, const float* gate, int gate_width,
+                                         int value_stride, const float* slopes, const float* sink_values,
                                          cudaStream_t stream) {
     if (tokens <= 0) return 0;
-    if (head_dim > 32 * MAX_DIM_PER_LANE || value_dim < 1 || value_dim > 32 * MAX_DIM_PER_LANE || heads % kv_heads)
+    if (gate && gate_width != 1 && gate_width != value_dim) return ME_ERR_ARGUMENT;
+    if (value_stride < value_dim) return ME_ERR_ARGUMENT;
+    if (head_dim > MAX_KEY_DIM || value_dim < 1 || value_dim > 32 * MAX_DIM_PER_LANE || heads % kv_heads)
         return ME_ERR_UNSUPPORTED;
     AttnArgs a{q, k_pages, v_pages, block_table, entry_of_token, positions, out, scale,
-               tokens, heads, kv_heads, head_dim, page_size, table_width, window, value_dim, sink, gate};
+               tokens, heads, kv_heads, head_dim, page_size, table_width, window, value_dim, sink, gate,
+               gate_width, value_stride, slopes, sink_values};
     const long long items = static_cast<long long>(tokens) * heads;
     const int blocks = static_cast<int>((items + ATTN_WARPS - 1) / ATTN_WARPS);
     const size_t smem = static_cast<size_t>(ATTN_WARPS) * head_dim * sizeof(float);

@@ -33,6 +33,7 @@ LIBRARIES = {
     "gemm_simt": "gemm_simt.cu",
     "attention_generic": "attention_generic.cu",
     "attention_biased": "attention_biased.cu",
+    "latent_attention": "latent_attention.cu",
     "linear_attention": "linear_attention.cu",
     "recurrent": "recurrent.cu",
     "routing": "routing.cu",

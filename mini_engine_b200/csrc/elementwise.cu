@@ -285,17 +285,125 @@ ME_EXPORT int me_add_rmsnorm(float* x, const float* pending, int splits, long lo
                : launch_add_rmsnorm<float, false>(x, pending, splits, stride, weight, eps, o, rows, count, hidden, stream, pending_scale, x_scale, keep_normed);
 }
 
+// -------------------------------------------------------------- residual sum + layer norm
+
+// One block per output row.  x_row = x[src] + add_bias + sum_s first[s][src] + sum_s second[s][src] (each sum in
+// ascending s); when `rows` is null and something was added the sum is written back to x.  Then
+// out = (x_row - mean) * rsqrt(var + eps) * weight + bias with var the mean of the squared deviations from the
+// mean (two passes over the row, which stays in shared memory), all in float32.  `second` is the output of a
+// second sublayer that read the same normalised input as the first (a parallel block); `add_bias` is the bias of
+// the first sublayer's output projection.  Column i goes to the partial sum of thread i % 256 in ascending
+// order, warps are added by a butterfly and then in ascending order: a row's statistics never depend on the batch.
+struct LayerNormArgs {
+    float* x;
+    const float* first;
+    int first_splits;
+    size_t first_stride;
+    const float* second;
+    int second_splits;
+    size_t second_stride;
+    const float* add_bias;
+    const float* weight;
+    const float* bias;
+    float eps;
+    void* out;
+    const int* rows;
+    int hidden;
+};
+
+__device__ __forceinline__ float block_sum_256(float v, float* scratch) {
+    v = warp_sum(v);
+    if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float total = 0.0f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) total += scratch[w];
+    __syncthreads();
+    return total;
+}
+
+template <typename OutT>
+__global__ void __launch_bounds__(256) add_layernorm_kernel(LayerNormArgs a) {
+    extern __shared__ float row_cache[];  // [hidden]
+    __shared__ float scratch[8];
+    const int out_row = blockIdx.x;
+    pdl_trigger();
+    const int src = a.rows ? a.rows[out_row] : out_row;
+    pdl_wait();
+    const size_t offset = static_cast<size_t>(src) * a.hidden;
+    float* x_row = a.x + offset;
+    const bool write_back = !a.rows && (a.first_splits > 0 || a.second_splits > 0 || a.add_bias != nullptr);
+    float sum = 0.0f;
+    for (int i = threadIdx.x; i < a.hidden; i += 256) {
+        float v = x_row[i];
+        if (a.first_splits > 0) {
+            float part = a.first[offset + i];
+            for (int s = 1; s < a.first_splits; ++s) part += a.first[s * a.first_stride + offset + i];
+            if (a.add_bias) part += a.add_bias[i];
+            v += part;
+        } else if (a.add_bias) {
+            v += a.add_bias[i];
+        }
+        if (a.second_splits > 0) {
+            float part = a.second[offset + i];
+            for (int s = 1; s < a.second_splits; ++s) part += a.second[s * a.second_stride + offset + i];
+            v += part;
+        }
+        row_cache[i] = v;
+        if (write_back) x_row[i] = v;
+        sum += v;
+    }
+    const float mean = block_sum_256(sum, scratch) / static_cast<float>(a.hidden);
+    float squares = 0.0f;
+    for (int i = threadIdx.x; i < a.hidden; i += 256) {
+        const float d = row_cache[i] - mean;
+        squares = fmaf(d, d, squares);
+    }
+    const float inv = rsqrtf(block_sum_256(squares, scratch) / static_cast<float>(a.hidden) + a.eps);
+    OutT* out_ptr = static_cast<OutT*>(a.out) + static_cast<size_t>(out_row) * a.hidden;
+    for (int i = threadIdx.x; i < a.hidden; i += 256)
+        out_ptr[i] = from_float<OutT>(fmaf((row_cache[i] - mean) * inv, a.weight[i], a.bias[i]));
+}
+
+ME_EXPORT int me_add_layernorm(float* x, const float* first, int first_splits, long long first_stride,
+                               const float* second, int second_splits, long long second_stride, const float* add_bias,
+                               const float* weight, const float* bias, float eps, void* out, int out_type,
+                               const int* rows, int count, int hidden, cudaStream_t stream) {
+    if (count <= 0) return 0;
+    const size_t smem = static_cast<size_t>(hidden) * sizeof(float);
+    if (smem > 200 * 1024) return ME_ERR_UNSUPPORTED;
+    if ((first_splits > 0 && first == nullptr) || (second_splits > 0 && second == nullptr)) return ME_ERR_ARGUMENT;
+    LayerNormArgs a{x, first, first_splits, (size_t)first_stride, second, second_splits, (size_t)second_stride,
+                    add_bias, weight, bias, eps, out, rows, hidden};
+    if (out_type == ME_BF16) {
+        auto kernel = add_layernorm_kernel<__nv_bfloat16>;
+        if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        return launch_kernel(kernel, count, 256, smem, stream, a);
+    }
+    auto kernel = add_layernorm_kernel<float>;
+    if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    return launch_kernel(kernel, count, 256, smem, stream, a);
+}
+
 // --------------------------------------------------------------------------------- SwiGLU
 
 // partial[s][t][0..inter) are gate sums, [inter..2*inter) up sums.  out = g * sigmoid(slope * g) * (u + offset)
 // with g = min(gate, limit) and u = clamp(up, -limit, limit) when limit > 0, else g = gate and u = up;
 // slope 1, no limit and offset 0 are silu(gate) * up.  With `group_weight [tokens][groups]` the features form
 // `groups` equal runs (the units of a routed feed-forward side by side) and feature i of token t is multiplied
-// by group_weight[t][i / group_size].
+// by group_weight[t][i / group_size].  `activation` 1 replaces g * sigmoid(slope * g) by the tanh form of GELU,
+// 0.5 g (1 + tanh(sqrt(2 / pi) (g + 0.044715 g^3))).
+enum : int { GATE_SIGMOID = 0, GATE_GELU_TANH = 1 };
+
+__device__ __forceinline__ float gate_activation(float g, float slope, int activation) {
+    if (activation == GATE_GELU_TANH) return 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
+    return g / (1.0f + expf(-slope * g));
+}
+
 template <typename OutT>
 __global__ void swiglu_kernel(const float* __restrict__ partial, int splits, size_t split_stride,
                               OutT* __restrict__ out, int tokens, int inter, float slope, float limit, float offset,
-                              const float* __restrict__ group_weight, int group_size, int groups) {
+                              const float* __restrict__ group_weight, int group_size, int groups, int activation) {
     const size_t total = static_cast<size_t>(tokens) * inter;
     pdl_trigger();
     pdl_wait();
@@ -313,7 +421,7 @@ __global__ void swiglu_kernel(const float* __restrict__ partial, int splits, siz
             gate = fminf(gate, limit);
             up = fminf(fmaxf(up, -limit), limit);
         }
-        const float activated = gate / (1.0f + expf(-slope * gate));
+        const float activated = gate_activation(gate, slope, activation);
         float value = activated * (up + offset);
         // routed units: feature i belongs to unit i / group_size, whose weight for this token may be zero
         if (group_weight != nullptr) value *= group_weight[t * groups + i / group_size];
@@ -325,7 +433,7 @@ __global__ void swiglu_kernel(const float* __restrict__ partial, int splits, siz
 template <typename OutT>
 __global__ void swiglu_vec_kernel(const float* __restrict__ partial, int splits, size_t split_stride,
                                   OutT* __restrict__ out, int tokens, int inter, float slope, float limit, float offset,
-                                  const float* __restrict__ group_weight, int group_size, int groups) {
+                                  const float* __restrict__ group_weight, int group_size, int groups, int activation) {
     const size_t quads = static_cast<size_t>(inter / 4);
     const size_t total = static_cast<size_t>(tokens) * quads;
     pdl_trigger();
@@ -351,7 +459,7 @@ __global__ void swiglu_vec_kernel(const float* __restrict__ partial, int splits,
                 g = fminf(g, limit);
                 u = fminf(fmaxf(u, -limit), limit);
             }
-            const float activated = g / (1.0f + expf(-slope * g));
+            const float activated = gate_activation(g, slope, activation);
             y[j] = activated * (u + offset);
             if (group_weight != nullptr) y[j] *= weight;
         }
@@ -361,8 +469,9 @@ __global__ void swiglu_vec_kernel(const float* __restrict__ partial, int splits,
 
 ME_EXPORT int me_swiglu(const float* partial, int splits, long long split_stride, void* out, int out_type,
                         int tokens, int inter, float slope, float limit, float offset, const float* group_weight,
-                        int group_size, cudaStream_t stream) {
+                        int group_size, int activation, cudaStream_t stream) {
     if (tokens <= 0) return 0;
+    if (activation != GATE_SIGMOID && activation != GATE_GELU_TANH) return ME_ERR_ARGUMENT;
     if (group_weight != nullptr && (group_size < 1 || inter % group_size)) return ME_ERR_ARGUMENT;
     const int groups = group_weight != nullptr ? inter / group_size : 0;
     const size_t total = static_cast<size_t>(tokens) * inter;
@@ -374,17 +483,17 @@ ME_EXPORT int me_swiglu(const float* partial, int splits, long long split_stride
         const int blocks = static_cast<int>(std::min<size_t>((total / 4 + threads - 1) / threads, 148 * 64));
         if (out_type == ME_BF16)
             return launch_kernel(swiglu_vec_kernel<__nv_bfloat16>, blocks, threads, 0, stream, partial, splits, (size_t)split_stride,
-                                 static_cast<__nv_bfloat16*>(out), tokens, inter, slope, limit, offset, group_weight, group_size, groups);
+                                 static_cast<__nv_bfloat16*>(out), tokens, inter, slope, limit, offset, group_weight, group_size, groups, activation);
         return launch_kernel(swiglu_vec_kernel<float>, blocks, threads, 0, stream, partial, splits, (size_t)split_stride,
-                             static_cast<float*>(out), tokens, inter, slope, limit, offset, group_weight, group_size, groups);
+                             static_cast<float*>(out), tokens, inter, slope, limit, offset, group_weight, group_size, groups, activation);
     }
     const int blocks = static_cast<int>(std::min<size_t>((total + threads - 1) / threads, 148 * 16));
     if (out_type == ME_BF16)
         return launch_kernel(swiglu_kernel<__nv_bfloat16>, blocks, threads, 0, stream, partial, splits,
                              (size_t)split_stride, static_cast<__nv_bfloat16*>(out), tokens, inter, slope, limit, offset,
-                             group_weight, group_size, groups);
+                             group_weight, group_size, groups, activation);
     return launch_kernel(swiglu_kernel<float>, blocks, threads, 0, stream, partial, splits, (size_t)split_stride,
-                         static_cast<float*>(out), tokens, inter, slope, limit, offset, group_weight, group_size, groups);
+                         static_cast<float*>(out), tokens, inter, slope, limit, offset, group_weight, group_size, groups, activation);
 }
 
 // ------------------------------------------------- per-head norm + rotary + cache write
@@ -815,7 +924,8 @@ ME_EXPORT int me_round_rows(const float* x, void* out, int out_type, int rows, i
 // and k over its kv_heads * head_dim columns; then each head's first rotary_dim elements are rotated, q goes to
 // q_out and k, v to the token's cache slot (or to dense buffers).  `gates` trailing columns (one per query
 // head in the models that have them) leave the kernel as sigmoid(sum) in gate_out[t][gates], float32.
-// kv_heads == 0: a layer that reads another layer's keys and values has no k and v columns.
+// kv_heads == 0: a layer that reads another layer's keys and values has no k and v columns.  `bias` (one value
+// per column of the row, gates included) is added to the sums first.
 struct WideQkvArgs {
     const float* qkv;  // [splits][tokens][row_width]
     int splits;
@@ -833,6 +943,7 @@ struct WideQkvArgs {
     void* v_dense;
     float* gate_out;
     int tokens, heads, kv_heads, head_dim, value_dim, page_size, rotary_dim, gates;
+    const float* bias;  // [row_width] added to the sums before anything else, or null
 };
 
 template <typename OutT>
@@ -851,6 +962,7 @@ __global__ void __launch_bounds__(256) qk_wide_norm_rope_store_kernel(WideQkvArg
     for (int i = threadIdx.x; i < a.row_width; i += 256) {
         float v = 0.0f;
         for (int s = 0; s < a.splits; ++s) v += src[s * a.split_stride + i];
+        if (a.bias) v += a.bias[i];
         row[i] = v;
         if (i < q_width) q_sq = fmaf(v, v, q_sq);
         else if (i < q_width + k_width) k_sq = fmaf(v, v, k_sq);
@@ -914,7 +1026,7 @@ ME_EXPORT int me_qk_wide_norm_rope_store(const float* qkv, int splits, long long
                                          const int* slot_mapping, void* q_out, void* k_pages, void* v_pages,
                                          void* k_dense, void* v_dense, float* gate_out, int out_type, int tokens,
                                          int heads, int kv_heads, int head_dim, int value_dim, int page_size,
-                                         int rotary_dim, int gates, cudaStream_t stream) {
+                                         int rotary_dim, int gates, const float* bias, cudaStream_t stream) {
     if (tokens <= 0) return 0;
     if (rotary_dim < 0 || rotary_dim > head_dim || rotary_dim % 2) return ME_ERR_ARGUMENT;
     if (row_width < (heads + kv_heads) * head_dim + kv_heads * value_dim + gates) return ME_ERR_ARGUMENT;
@@ -923,7 +1035,7 @@ ME_EXPORT int me_qk_wide_norm_rope_store(const float* qkv, int splits, long long
     if (smem > 200 * 1024) return ME_ERR_UNSUPPORTED;
     WideQkvArgs a{qkv, splits, (size_t)split_stride, row_width, q_weight, k_weight, eps, reinterpret_cast<const float2*>(cos_sin),
                   slot_mapping, q_out, k_pages, v_pages, k_dense, v_dense, gate_out, tokens, heads, kv_heads, head_dim,
-                  value_dim, page_size, rotary_dim, gates};
+                  value_dim, page_size, rotary_dim, gates, bias};
     if (out_type == ME_BF16) {
         auto kernel = qk_wide_norm_rope_store_kernel<__nv_bfloat16>;
         if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);

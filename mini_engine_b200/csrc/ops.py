@@ -238,15 +238,67 @@ def add_rmsnorm(
     _check(code, "add_rmsnorm")
 
 
+GATE_ACTIVATIONS = {"silu": 0, "gelu_tanh": 1}
+
+
+def add_layernorm(
+    x: torch.Tensor,
+    pending: torch.Tensor | None,
+    weight: torch.Tensor,
+    bias: torch.Tensor,
+    eps: float,
+    out: torch.Tensor,
+    rows: torch.Tensor | None = None,
+    pending_more: torch.Tensor | None = None,
+    pending_bias: torch.Tensor | None = None,
+) -> None:
+    """``x += pending_bias + sum_s pending[s] + sum_s pending_more[s]`` (in place, float32) and ``out = (x - mean) /
+    sqrt(var + eps) * weight + bias`` with the variance as the mean of the squared deviations.  With ``rows`` only
+    ``x[rows]`` (+ the pending sums) are normalised into ``out[0..len(rows))`` and ``x`` is not modified."""
+    _need(x, torch.float32, "x"), _need(weight, torch.float32, "weight"), _need(bias, torch.float32, "bias"), _need(out, None, "out")
+    hidden = x.shape[-1]
+    sums = []
+    for name, part in (("pending", pending), ("pending_more", pending_more)):
+        if part is None:
+            sums += [None, 0, 0]
+            continue
+        _need(part, torch.float32, name)
+        if part.shape[1:] != x.shape:
+            raise KernelError(f"{name} {tuple(part.shape)} does not fit x {tuple(x.shape)}")
+        sums += [part, part.shape[0], part.stride(0)]
+    if weight.shape != (hidden,) or bias.shape != (hidden,) or out.shape[-1] != hidden:
+        raise KernelError("add_layernorm: weight/bias/out width does not match x")
+    if pending_bias is not None:
+        _need(pending_bias, torch.float32, "pending_bias")
+        if pending_bias.shape != (hidden,):
+            raise KernelError("add_layernorm: pending_bias must have one value per column")
+    count = x.shape[0] if rows is None else rows.shape[0]
+    if rows is not None:
+        _need(rows, torch.int32, "rows")
+    fn = _fn(
+        "elementwise",
+        "me_add_layernorm",
+        [c_void_p, c_void_p, c_int, c_longlong, c_void_p, c_int, c_longlong, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p],
+    )
+    code = fn(
+        _ptr(x), _ptr(sums[0]), sums[1], sums[2], _ptr(sums[3]), sums[4], sums[5], _ptr(pending_bias), _ptr(weight), _ptr(bias),
+        float(eps), _ptr(out), _type_code(out.dtype), _ptr(rows), count, hidden, _stream(),
+    )  # fmt: skip
+    _check(code, "add_layernorm")
+
+
 def swiglu(
     partials: torch.Tensor, out: torch.Tensor, slope: float = 1.0, limit: float | None = None, offset: float = 0.0,
-    group_weight: torch.Tensor | None = None,
+    group_weight: torch.Tensor | None = None, activation: str = "silu",
 ) -> None:
     """``out = g * sigmoid(slope * g) * (u + offset)`` where gate/up are the halves of ``sum_s
     partials[s]``, ``g = min(gate, limit)`` and ``u = clamp(up, -limit, limit)`` when a limit is
     given, else ``g = gate``, ``u = up``.  The defaults are ``silu(gate) * up``.  With ``group_weight``
     (float32 ``[T, groups]``) the features form ``groups`` equal runs and feature ``i`` of token ``t`` is
-    multiplied by ``group_weight[t, i // (inter / groups)]`` (routed units side by side)."""
+    multiplied by ``group_weight[t, i // (inter / groups)]`` (routed units side by side).  ``activation``
+    ``"gelu_tanh"`` puts ``0.5 g (1 + tanh(sqrt(2 / pi) (g + 0.044715 g^3)))`` in the place of ``g * sigmoid(slope * g)``."""
+    if activation not in GATE_ACTIVATIONS:
+        raise KernelError(f"swiglu: activation must be one of {sorted(GATE_ACTIVATIONS)}, got {activation!r}")
     _need(partials, torch.float32, "partials"), _need(out, None, "out")
     splits, tokens, width = partials.shape
     inter = width // 2
@@ -260,9 +312,10 @@ def swiglu(
         if group_weight.dim() != 2 or group_weight.shape[0] != tokens or inter % group_weight.shape[1]:
             raise KernelError(f"swiglu: group_weight {tuple(group_weight.shape)} does not fit {tokens} tokens of {inter} features")
         group_size = inter // group_weight.shape[1]
-    fn = _fn("elementwise", "me_swiglu", [c_void_p, c_int, c_longlong, c_void_p, c_int, c_int, c_int, c_float, c_float, c_float, c_void_p, c_int, c_void_p])
+    fn = _fn("elementwise", "me_swiglu", [c_void_p, c_int, c_longlong, c_void_p, c_int, c_int, c_int, c_float, c_float, c_float, c_void_p, c_int, c_int, c_void_p])
     code = fn(_ptr(partials), splits, partials.stride(0), _ptr(out), _type_code(out.dtype), tokens, inter,
-              float(slope), float(limit or 0.0), float(offset), _ptr(group_weight), group_size, _stream())  # fmt: skip
+              float(slope), float(limit or 0.0), float(offset), _ptr(group_weight), group_size,
+              GATE_ACTIVATIONS[activation], _stream())  # fmt: skip
     _check(code, "swiglu")
 
 
@@ -395,29 +448,49 @@ def gemm_tensor_core_swiglu(plan, x: torch.Tensor, act: torch.Tensor) -> None:
 def paged_attention_generic(
     q, k_pages, v_pages, block_table, entry_of_token, positions, out, heads, kv_heads, head_dim, scale, window,
     value_dim: int | None = None, sink: bool = False, gate: torch.Tensor | None = None,
+    slopes: torch.Tensor | None = None, sink_values: torch.Tensor | None = None,
 ) -> None:
     """One warp per (token, head), any head size; ``value_dim``: width of a value head when it differs;
-    ``sink``: one more participant of score zero and no value in the softmax; ``gate`` (float32 ``[T,
-    heads]``): a multiplier on each head's output."""
+    ``sink``: one more participant of score zero and no value in the softmax, or of the learned score
+    ``sink_values[h]`` (float32 ``[heads]``); ``gate`` (float32 ``[T, heads]`` or ``[T, heads * value_dim]``): a
+    multiplier on each head's output, or on each of its elements; ``slopes`` (float32 ``[heads]``): ``slopes[h] *
+    (p - j)`` is taken off the scaled score of query ``p`` and key ``j``.  ``v_pages=None``: the values are the first
+    ``value_dim`` elements of the key rows."""
     value_dim = head_dim if value_dim is None else value_dim
+    gate_width = 1
     if gate is not None:
         _need(gate, torch.float32, "gate")
-        if gate.shape != (q.shape[0], heads):
-            raise KernelError("gate must be [tokens, heads]")
-    if k_pages.shape[1:] != (kv_heads, k_pages.shape[2], head_dim) or v_pages.shape[1:] != (kv_heads, k_pages.shape[2], value_dim):
-        raise KernelError(f"pages {tuple(k_pages.shape)}, {tuple(v_pages.shape)} do not fit the head sizes")
+        if gate.shape == (q.shape[0], heads * value_dim) and value_dim > 1:
+            gate_width = value_dim
+        elif gate.shape != (q.shape[0], heads):
+            raise KernelError("gate must be [tokens, heads] or [tokens, heads * value_dim]")
+    for name, vector in (("slopes", slopes), ("sink_values", sink_values)):
+        if vector is not None:
+            _need(vector, torch.float32, name)
+            if vector.shape != (heads,):
+                raise KernelError(f"{name} must have one value per head")
+    value_stride = value_dim
+    if v_pages is None:
+        if value_dim > head_dim:
+            raise KernelError("values inside the key rows cannot be wider than the keys")
+        v_pages, value_stride = k_pages, head_dim
+    elif v_pages.shape[1:] != (kv_heads, k_pages.shape[2], value_dim):
+        raise KernelError(f"value pages {tuple(v_pages.shape)} do not fit the head sizes")
+    if k_pages.shape[1:] != (kv_heads, k_pages.shape[2], head_dim):
+        raise KernelError(f"key pages {tuple(k_pages.shape)} do not fit the head sizes")
     _need(q, None, "q"), _need(out, q.dtype, "out"), _need(k_pages, q.dtype, "k_pages"), _need(v_pages, q.dtype, "v_pages")
     _need(block_table, torch.int32, "block_table"), _need(entry_of_token, torch.int32, "entry_of_token")
     _need(positions, torch.int32, "positions")
     fn = _fn(
         "attention_generic",
         "me_paged_attention_generic",
-        [c_void_p] * 7 + [c_int, c_float] + [c_int] * 9 + [c_void_p, c_void_p],
+        [c_void_p] * 7 + [c_int, c_float] + [c_int] * 9 + [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p],
     )
     code = fn(
         _ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(block_table), _ptr(entry_of_token), _ptr(positions), _ptr(out),
         _type_code(q.dtype), scale, q.shape[0], heads, kv_heads, head_dim, k_pages.shape[2], block_table.shape[1],
-        window, value_dim, 1 if sink else 0, _ptr(gate), _stream(),
+        window, value_dim, 1 if (sink or sink_values is not None) else 0, _ptr(gate), gate_width, value_stride,
+        _ptr(slopes), _ptr(sink_values), _stream(),
     )  # fmt: skip
     _check(code, "paged_attention_generic")
 
@@ -425,12 +498,15 @@ def paged_attention_generic(
 def paged_attention(
     *, q, k_pages, v_pages, block_table, ctx, out, heads: int, kv_heads: int, head_dim: int, scale: float, window: int,
     value_dim: int | None = None, sink: bool = False, gate: torch.Tensor | None = None,
+    slopes: torch.Tensor | None = None, sink_values: torch.Tensor | None = None,
 ) -> None:  # fmt: skip
     """Causal attention of the batch's new tokens over their requests' cached keys (the new
     tokens' own keys are already in the cache).  Chooses the kernel by dtype and sizes.  ``value_dim``,
-    ``sink`` and ``gate`` as in :func:`paged_attention_generic`; value heads of another width than the key
-    heads take that kernel."""
-    if q.dtype == torch.bfloat16 and value_dim in (None, head_dim):
+    ``sink``, ``gate``, ``slopes`` and ``sink_values`` as in :func:`paged_attention_generic`; value heads of another
+    width than the key heads, values inside the key rows (``v_pages=None``), a gate per element, a distance bias
+    and learned sinks take that kernel."""
+    plain = slopes is None and sink_values is None and v_pages is not None and (gate is None or gate.shape[1] == heads)
+    if plain and q.dtype == torch.bfloat16 and value_dim in (None, head_dim):
         if attention_bf16.supports(head_dim, heads, kv_heads):
             attention_bf16.paged_attention(
                 q, k_pages, v_pages, block_table, ctx, out, heads, kv_heads, head_dim, scale, window, sink=sink, gate=gate
@@ -438,8 +514,80 @@ def paged_attention(
             return
     paged_attention_generic(
         q, k_pages, v_pages, block_table, ctx.entry_of_token, ctx.positions, out, heads, kv_heads, head_dim,
-        scale, window, value_dim=value_dim, sink=sink, gate=gate,
+        scale, window, value_dim=value_dim, sink=sink, gate=gate, slopes=slopes, sink_values=sink_values,
     )  # fmt: skip
+
+
+def latent_down_finish(
+    *, down: torch.Tensor, q_rank: int, kv_rank: int, rot_dim: int, q_weight: torch.Tensor, kv_weight: torch.Tensor,
+    eps: float, cos_sin: torch.Tensor | None, slot_mapping: torch.Tensor, q_latent: torch.Tensor, k_pages: torch.Tensor,
+    gates: int = 0, gate_out: torch.Tensor | None = None,
+) -> None:  # fmt: skip
+    """The row ``[query latent | c | k_rot | gates]`` of a fused down projection (``down``: ``[S, T, width]`` float32
+    partial sums): RMS norm of the query latent into ``q_latent [T, q_rank]`` and of ``c`` (each with its weight),
+    rotation of the first ``rotary_dim`` elements of ``k_rot``, the write of ``[c | k_rot]`` to the token's slot of
+    ``k_pages [pages, 1, page_size, kv_rank + rot_dim]``, and ``sigmoid`` of the gates into ``gate_out [T, gates]``."""
+    _need(down, torch.float32, "down"), _need(q_latent, None, "q_latent"), _need(k_pages, q_latent.dtype, "k_pages")
+    _need(q_weight, torch.float32, "q_weight"), _need(kv_weight, torch.float32, "kv_weight")
+    _need(slot_mapping, torch.int32, "slot_mapping")
+    splits, tokens, width = down.shape
+    if width != q_rank + kv_rank + rot_dim + gates:
+        raise KernelError(f"the down projection's width {width} is not q_rank + kv_rank + rot_dim + gates")
+    if q_weight.shape != (q_rank,) or kv_weight.shape != (kv_rank,) or q_latent.shape != (tokens, q_rank):
+        raise KernelError("latent_down_finish: norm weights or q_latent do not fit the ranks")
+    if k_pages.dim() != 4 or k_pages.shape[1] != 1 or k_pages.shape[3] != kv_rank + rot_dim:
+        raise KernelError(f"key pages {tuple(k_pages.shape)} are not [pages, 1, page_size, kv_rank + rot_dim]")
+    rotary_dim = 0
+    if cos_sin is not None:
+        _need(cos_sin, torch.float32, "cos_sin")
+        rotary_dim = 2 * cos_sin.shape[1] if cos_sin.dim() == 3 else -1
+        if cos_sin.dim() != 3 or cos_sin.shape[0] != tokens or cos_sin.shape[2] != 2 or not 2 <= rotary_dim <= rot_dim:
+            raise KernelError(f"cos_sin {tuple(cos_sin.shape)} is not [tokens, rotary_dim / 2, 2] with rotary_dim <= rot_dim")
+    if gates:
+        _need(gate_out, torch.float32, "gate_out")
+        if gate_out.shape != (tokens, gates):
+            raise KernelError("gate_out must be [tokens, gates]")
+    fn = _fn("latent_attention", "me_latent_down_finish",
+             [c_void_p, c_int, c_longlong, c_int, c_void_p, c_void_p, c_float] + [c_void_p] * 5 + [c_int] * 7 + [c_void_p])  # fmt: skip
+    code = fn(
+        _ptr(down), splits, down.stride(0), width, _ptr(q_weight), _ptr(kv_weight), float(eps), _ptr(cos_sin),
+        _ptr(slot_mapping), _ptr(q_latent), _ptr(k_pages), _ptr(gate_out), _type_code(q_latent.dtype), tokens, q_rank,
+        kv_rank, rot_dim, rotary_dim, gates, _stream(),
+    )  # fmt: skip
+    _check(code, "latent_down_finish")
+
+
+def head_product(
+    x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, *, tail: int = 0, cos_sin: torch.Tensor | None = None,
+) -> None:  # fmt: skip
+    """``out[t, h, n] = sum_k x[t, h, k] * weight[h, k, n]`` for every head, ascending ``k``, float32 sums.  ``x`` is
+    ``[T, heads * (inner + tail)]`` in the dtype of ``weight``, or float32 partial sums ``[S, T, heads * (inner +
+    tail)]``; ``out`` is ``[T, heads * (outs + tail)]``.  The ``tail`` last columns of every head of ``x`` are appended to
+    the head's output, the first ``rotary_dim`` of them rotated by ``cos_sin [T, rotary_dim / 2, 2]``."""
+    _need(weight, None, "weight"), _need(out, weight.dtype, "out"), _need(x, None, "x")
+    heads, inner, outs = weight.shape
+    if x.dim() == 3:
+        _need(x, torch.float32, "x")
+        splits, stride, tokens = x.shape[0], x.stride(0), x.shape[1]
+    else:
+        splits, stride, tokens = 1, 0, x.shape[0]
+        if x.dtype not in (torch.float32, weight.dtype):
+            raise KernelError("head_product: x must be float32 or have the dtype of the weight")
+    if x.shape[-1] != heads * (inner + tail) or out.shape != (tokens, heads * (outs + tail)):
+        raise KernelError(f"head_product: {tuple(x.shape)} x {tuple(weight.shape)} -> {tuple(out.shape)} with a tail of {tail}")
+    rotary_dim = 0
+    if cos_sin is not None:
+        _need(cos_sin, torch.float32, "cos_sin")
+        rotary_dim = 2 * cos_sin.shape[1] if cos_sin.dim() == 3 else -1
+        if cos_sin.dim() != 3 or cos_sin.shape[0] != tokens or cos_sin.shape[2] != 2 or not 2 <= rotary_dim <= tail:
+            raise KernelError(f"cos_sin {tuple(cos_sin.shape)} is not [tokens, rotary_dim / 2, 2] with rotary_dim <= tail")
+    fn = _fn("latent_attention", "me_head_product",
+             [c_void_p, c_int, c_int, c_longlong, c_void_p, c_void_p, c_void_p] + [c_int] * 7 + [c_void_p])  # fmt: skip
+    code = fn(
+        _ptr(x), _type_code(x.dtype), splits, stride, _ptr(weight), _ptr(cos_sin), _ptr(out), _type_code(weight.dtype),
+        tokens, heads, inner, outs, tail, rotary_dim, _stream(),
+    )  # fmt: skip
+    _check(code, "head_product")
 
 
 def biased_attention(
@@ -634,12 +782,13 @@ def qk_wide_norm_rope_store(
     k_weight: torch.Tensor | None, eps: float, cos_sin: torch.Tensor | None, q_out: torch.Tensor, page_size: int,
     slot_mapping: torch.Tensor | None = None, k_pages: torch.Tensor | None = None, v_pages: torch.Tensor | None = None,
     k_dense: torch.Tensor | None = None, v_dense: torch.Tensor | None = None, gates: int = 0,
-    gate_out: torch.Tensor | None = None,
+    gate_out: torch.Tensor | None = None, bias: torch.Tensor | None = None,
 ) -> None:  # fmt: skip
     """RMSNorm of q over all its ``heads * head_dim`` columns at once (weight of that size) and of k over its
     ``kv_heads * head_dim`` columns, rotation of the first ``rotary_dim`` elements of every head, and the write
     of k and v to their cache slots (or dense buffers).  ``qkv`` is ``[S, T, width]`` float32 partial sums with the
-    columns ``[q | k | v | gates]``; the ``gates`` trailing columns come out as ``sigmoid`` in ``gate_out [T, gates]``."""
+    columns ``[q | k | v | gates]``; the ``gates`` trailing columns come out as ``sigmoid`` in ``gate_out [T, gates]``.
+    ``bias`` (float32, one value per column of ``qkv``) is added to the sums before anything else."""
     _need(qkv, torch.float32, "qkv"), _need(q_out, None, "q_out")
     splits, tokens, width = qkv.shape
     if width != (heads + kv_heads) * head_dim + kv_heads * value_dim + gates:
@@ -670,13 +819,17 @@ def qk_wide_norm_rope_store(
         _need(gate_out, torch.float32, "gate_out")
         if gate_out.shape != (tokens, gates):
             raise KernelError("gate_out must be [tokens, gates]")
+    if bias is not None:
+        _need(bias, torch.float32, "bias")
+        if bias.shape != (width,):
+            raise KernelError(f"bias {tuple(bias.shape)} does not fit the {width} columns of qkv")
     fn = _fn("elementwise", "me_qk_wide_norm_rope_store",
-             [c_void_p, c_int, c_longlong, c_int, c_void_p, c_void_p, c_float] + [c_void_p] * 8 + [c_int] * 9 + [c_void_p])  # fmt: skip
+             [c_void_p, c_int, c_longlong, c_int, c_void_p, c_void_p, c_float] + [c_void_p] * 8 + [c_int] * 9 + [c_void_p, c_void_p])  # fmt: skip
     code = fn(
         _ptr(qkv), splits, qkv.stride(0), width, _ptr(q_weight), _ptr(k_weight if kv_heads else None), float(eps),
         _ptr(cos_sin), _ptr(slot_mapping if kv_heads else None), _ptr(q_out), _ptr(k_pages), _ptr(v_pages), _ptr(k_dense),
         _ptr(v_dense), _ptr(gate_out), _type_code(q_out.dtype), tokens, heads, kv_heads, head_dim, value_dim, page_size,
-        rotary_dim, gates, _stream(),
+        rotary_dim, gates, _ptr(bias), _stream(),
     )  # fmt: skip
     _check(code, "qk_wide_norm_rope_store")
 

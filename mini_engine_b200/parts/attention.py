@@ -28,6 +28,14 @@ participant of score zero and no value to every softmax, ``p_j = exp(s_j) / (1 +
 ``head_gate`` multiplies head ``h``'s output by ``sigmoid(W_g x)_h`` with a learned ``W_g [heads,
 hidden]`` that runs as extra rows of the fused q/k/v product.  A layer that reads another entry's cache
 (``reads_shared_cache``) may have a window of its own.
+
+And four for designs without rotation whose positions enter through the scores: ``distance_bias="linear"`` takes
+``slope_h * (p - j)`` off the scaled score of query ``p`` and key ``j``, with the fixed slopes ``slope_h = 2 **
+(-linear_bias_span * (h + 1) / heads)``; ``softmax_sink="learned"`` makes the silent participant's score a learned
+number per head (tensor ``sink``), ``p_j = exp(s_j) / (exp(sink_h) + sum_i exp(s_i))``; ``element_gate`` multiplies
+the concatenated heads element by element with ``sigmoid(W_g x)``, ``W_g [heads * value_dim, hidden]``, again as rows
+of the fused product; ``o_bias`` gives the output projection a bias, which the block hands to the norm that adds
+the projection's partial sums.  With these, ``qkv_bias`` may be combined.
 """
 
 from __future__ import annotations
@@ -71,28 +79,42 @@ class GroupedQueryAttention(Mixer):
         names: Mapping[str, str] | None = None,
         value_dim: int | None = None,
         keep_first: int = 0,
-        distance_bias: bool = False,
+        distance_bias: bool | str = False,
         talking_heads: bool = False,
         qk_norm_scope: str = "head",
-        softmax_sink: bool = False,
+        softmax_sink: bool | str = False,
         head_gate: bool = False,
+        element_gate: bool = False,
+        o_bias: bool = False,
+        linear_bias_span: float = 8.0,
     ):
         if num_heads % kv_heads:
             raise ValueError(f"num_heads ({num_heads}) must be a multiple of kv_heads ({kv_heads})")
         self.value_dim = head_dim if value_dim is None else int(value_dim)
         self.keep_first = int(keep_first) if window else 0
+        if distance_bias not in (False, True, "log", "linear") or softmax_sink not in (False, True, "learned"):
+            raise ValueError("distance_bias is False, 'log' or 'linear'; softmax_sink is False, True or 'learned'")
+        self.linear_bias = distance_bias == "linear"
+        self.linear_bias_span = float(linear_bias_span)
+        self.learned_sink = softmax_sink == "learned"
+        distance_bias = bool(distance_bias) and not self.linear_bias  # below: the logarithmic form with learned constants
         self.distance_bias, self.talking_heads = bool(distance_bias), bool(talking_heads)
         # Whether the step runs in the kernels that know these options (any head size) or in the plain ones.
         if qk_norm_scope not in ("head", "projection"):
             raise ValueError(f"qk_norm_scope must be 'head' or 'projection', got {qk_norm_scope!r}")
         self.wide_norm = qk_norm_scope == "projection" and qk_norm_eps is not None
-        self.sink, self.head_gate = bool(softmax_sink), bool(head_gate)
+        self.sink, self.head_gate, self.element_gate = bool(softmax_sink), bool(head_gate), bool(element_gate)
+        if self.head_gate and self.element_gate:
+            raise ValueError("a mixer gates its heads or its elements, not both")
+        self.has_output_bias = bool(o_bias)
         # Whether q, k, v (and the gates) leave the fused product through the kernel that normalises whole projections.
-        self.wide_store = self.wide_norm or self.head_gate
-        if self.head_gate and qk_norm_eps is not None and not self.wide_norm:
-            raise ValueError("head_gate comes with qk_norm_scope='projection' or without q/k norms")
-        if (self.wide_store or self.sink) and (keep_first or distance_bias or talking_heads or qkv_bias):
-            raise ValueError("qk_norm_scope='projection', softmax_sink and head_gate do not combine with keep_first, distance_bias, talking_heads or biases")
+        self.wide_store = self.wide_norm or self.head_gate or self.element_gate or self.linear_bias
+        if (self.head_gate or self.element_gate or self.linear_bias) and qk_norm_eps is not None and not self.wide_norm:
+            raise ValueError("gates and the linear distance bias come with qk_norm_scope='projection' or without q/k norms")
+        if (self.wide_store or self.sink) and (keep_first or distance_bias or talking_heads):
+            raise ValueError("qk_norm_scope='projection', softmax_sink, gates and the linear distance bias do not combine with keep_first, the logarithmic distance_bias or talking_heads")
+        if qkv_bias and self.sink and not self.wide_store:
+            raise ValueError("biases with a sink need the projection-wide store (a gate, a linear bias or qk_norm_scope='projection')")
         self.extended = bool(
             (self.value_dim != head_dim and not (self.wide_store or self.sink)) or self.keep_first or distance_bias or talking_heads
         )
@@ -132,12 +154,17 @@ class GroupedQueryAttention(Mixer):
             "r2": "distance_bias.r2",
             "talk": "talking_heads.weight",
             "gate": "gate_proj.weight",
+            "sink": "sink",
+            "o_bias": "o_proj.bias",
         }
         self.names = {key: prefix + (names or {}).get(key, value) for key, value in defaults.items()}
         self.position = None
         if position_encoding is not None:
             self.position = build_part("position_encoding", position_encoding, prefix, hidden_size)
         self.r1 = self.r2 = self.talk = None
+        self.gates = num_heads if self.head_gate else num_heads * self.value_dim if self.element_gate else 0
+        self.slopes: torch.Tensor | None = None
+        self.sink_values: torch.Tensor | None = None
         self.qkv: Linear | None = None
         self.out: Linear | None = None
         self.q_norm: torch.Tensor | None = None
@@ -163,8 +190,12 @@ class GroupedQueryAttention(Mixer):
             specs += [WeightSpec(n[key], (self.heads,), role="vector", init="positive") for key in ("r1", "r2")]
         if self.talking_heads:
             specs.append(WeightSpec(n["talk"], (self.heads, self.heads), role="vector", init="ones_normal"))
-        if self.head_gate:
-            specs.append(WeightSpec(n["gate"], (self.heads, self.hidden)))
+        if self.gates:
+            specs.append(WeightSpec(n["gate"], (self.gates, self.hidden)))
+        if self.learned_sink:
+            specs.append(WeightSpec(n["sink"], (self.heads,), role="vector", init="small_normal"))
+        if self.has_output_bias:
+            specs.append(WeightSpec(n["o_bias"], (self.hidden,), role="vector", init="small_normal"))
         if self.qk_norm_eps is not None:
             q_len, k_len = (self.heads * d, self.kv_heads * d) if self.wide_norm else (d, d)
             specs.append(WeightSpec(n["q_norm"], (q_len,), role="vector", init="ones_normal"))
@@ -174,7 +205,7 @@ class GroupedQueryAttention(Mixer):
             specs.append(WeightSpec(n["q_bias"], (self.heads * d,), role="vector"))
             if not self.reads_shared_cache:
                 specs.append(WeightSpec(n["k_bias"], (self.kv_heads * d,), role="vector"))
-                specs.append(WeightSpec(n["v_bias"], (self.kv_heads * d,), role="vector"))
+                specs.append(WeightSpec(n["v_bias"], (self.kv_heads * self.value_dim,), role="vector"))
         return specs + (self.position.weight_specs() if self.position is not None else [])
 
     def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
@@ -182,7 +213,7 @@ class GroupedQueryAttention(Mixer):
         rows = [tensors[n["q"]]]
         if not self.reads_shared_cache:
             rows += [tensors[n["k"]], tensors[n["v"]]]
-        if self.head_gate:
+        if self.gates:
             rows.append(tensors[n["gate"]])
         self.qkv = Linear(torch.cat(rows, dim=0).contiguous() if len(rows) > 1 else rows[0])
         self.out = Linear(tensors[n["o"]])
@@ -193,7 +224,16 @@ class GroupedQueryAttention(Mixer):
             parts = [tensors[n["q_bias"]]]
             if not self.reads_shared_cache:
                 parts += [tensors[n["k_bias"]], tensors[n["v_bias"]]]
+            if self.gates:  # the gate rows of the fused product have no bias
+                parts.append(torch.zeros(self.gates, dtype=parts[0].dtype, device=parts[0].device))
             self.bias = torch.cat(parts).contiguous()
+        if self.has_output_bias:
+            self.output_bias = tensors[n["o_bias"]]
+        if self.learned_sink:
+            self.sink_values = tensors[n["sink"]]
+        if self.linear_bias:
+            slopes = [2.0 ** (-self.linear_bias_span * (h + 1) / self.heads) for h in range(self.heads)]
+            self.slopes = torch.tensor(slopes, dtype=torch.float32, device=tensors[n["q"]].device)
         if self.distance_bias:
             self.r1, self.r2 = tensors[n["r1"]], tensors[n["r2"]]
         if self.talking_heads:
@@ -276,12 +316,12 @@ class GroupedQueryAttention(Mixer):
         kv_in = 0 if self.reads_shared_cache else self.kv_heads
         if self.position is not None and table is None:
             raise ValueError("these attention options take a rotation that the fused kernel applies, or none")
-        gate = ctx.buffer("attn.gate", (tokens, self.heads), torch.float32) if self.head_gate else None
+        gate = ctx.buffer("attn.gate", (tokens, self.gates), torch.float32) if self.gates else None
         if self.wide_store:
             args: dict[str, Any] = dict(
                 qkv=qkv, heads=self.heads, kv_heads=kv_in, head_dim=d, value_dim=self.value_dim, q_weight=self.q_norm,
                 k_weight=self.k_norm, eps=self.qk_norm_eps or 0.0, cos_sin=table, q_out=q, page_size=ctx.page_size,
-                gates=self.heads if self.head_gate else 0, gate_out=gate,
+                gates=self.gates, gate_out=gate, bias=self.bias,
             )  # fmt: skip
             if kv_in and not cache.writes:  # this execution reads another entry's cache: its own keys and values are not kept
                 unused_k = ctx.buffer("attn.k_new", (tokens, kv_in * d), ctx.dtype)
@@ -299,6 +339,6 @@ class GroupedQueryAttention(Mixer):
         ops.paged_attention(
             q=q, k_pages=cache.k, v_pages=cache.v, block_table=ctx.block_tables[cache.group], ctx=ctx, out=out,
             heads=self.heads, kv_heads=self.kv_heads, head_dim=d, scale=self.scale, window=self.window or 0,
-            value_dim=self.value_dim, sink=self.sink, gate=gate,
+            value_dim=self.value_dim, sink=self.sink, gate=gate, slopes=self.slopes, sink_values=self.sink_values,
         )  # fmt: skip
         return self.out.forward(out, ctx, "attn.o")

@@ -39,8 +39,9 @@ class PagedCacheSpec:
     are ever read and pages wholly behind the window are given back while the request runs.
     With a window, ``keep_first`` tokens at the start of the sequence stay readable for good (their
     pages are never given back).  ``value_dim`` is the width of a value head when it differs from
-    ``head_dim``.  Mixers with an equal spec share one cache group (one page pool, one block table
-    per request).
+    ``head_dim``; 0 says that the values are a part of the key rows (a cache of one latent row per token
+    that serves as key and as value), so that no value pages are kept.  Mixers with an equal spec share
+    one cache group (one page pool, one block table per request).
     """
 
     kv_heads: int
@@ -74,23 +75,34 @@ class Residual:
     ``pending_scale`` (float32 ``[hidden]``, a layer scale) their sum is multiplied column by column
     before it is added.  ``rounded`` is ``x`` in the compute dtype when a part has already made that
     copy (an embedding, or a norm that wrote its result back to ``x``), for a sublayer that reads the
-    stream itself; whoever changes ``x`` sets or clears it.
+    stream itself; whoever changes ``x`` sets or clears it.  ``pending_bias`` (float32 ``[hidden]``) is the
+    bias of the output projection whose partial sums are pending, added with them.  ``pending_more`` is
+    the output of a second sublayer that read the same input as the first (sublayers side by side),
+    ``[S', T, hidden]``, added as well.  A norm that does not know one of these must refuse it.
     """
 
     x: torch.Tensor
     pending: torch.Tensor | None = None
     pending_scale: torch.Tensor | None = None
     rounded: torch.Tensor | None = None
+    pending_bias: torch.Tensor | None = None
+    pending_more: torch.Tensor | None = None
 
-    def add(self, delta: torch.Tensor, scale: torch.Tensor | None = None) -> None:
+    def add(self, delta: torch.Tensor, scale: torch.Tensor | None = None, bias: torch.Tensor | None = None) -> None:
         if self.pending is not None:
             raise RuntimeError("a pending output must be consumed by a norm before the next is set")
         if delta.dim() == 2:
             delta = delta.unsqueeze(0)
-        self.pending, self.pending_scale = delta, scale
+        self.pending, self.pending_scale, self.pending_bias = delta, scale, bias
+
+    def add_beside(self, delta: torch.Tensor) -> None:
+        """The output of a sublayer that ran beside the one whose output is pending."""
+        if self.pending is None or self.pending_more is not None or self.pending_scale is not None:
+            raise RuntimeError("a second output goes beside exactly one pending output without a scale")
+        self.pending_more = delta.unsqueeze(0) if delta.dim() == 2 else delta
 
     def clear(self) -> None:
-        self.pending = self.pending_scale = None
+        self.pending = self.pending_scale = self.pending_bias = self.pending_more = None
 
 
 @dataclass
@@ -207,6 +219,12 @@ class PositionEncoding(Part):
 
 
 class Mixer(Part):
+    # The bias of the mixer's output projection (float32 ``[hidden]``) when it has one: `forward` returns the
+    # product's partial sums without it, and the block hands it to the norm that adds them (``Residual.add``).
+    # A block that does not (``Block.adds_output_bias``) cannot hold such a mixer.
+    output_bias: torch.Tensor | None = None
+    has_output_bias = False
+
     def paged_cache(self) -> PagedCacheSpec | None:
         return None
 
@@ -254,8 +272,11 @@ class Block(Part):
     exactly those (``LayerSpec.named_norms``), and they arrive as ``self.norms[name]``."""
 
     NORMS: tuple[str, ...] = ("mixer", "feed_forward")
+    adds_output_bias = False  # whether the arrangement hands `Mixer.output_bias` on with the mixer's output
 
     def __init__(self, mixer: Mixer, feed_forward: FeedForward, norms: Mapping[str, Norm]):
+        if getattr(mixer, "has_output_bias", False) and not self.adds_output_bias:
+            raise ValueError(f"{type(self).__name__} does not add the bias of its mixer's output projection")
         if set(norms) != set(self.NORMS):
             raise ValueError(
                 f"{type(self).__name__} wants the norms {sorted(self.NORMS)}, the layer names {sorted(norms)}"

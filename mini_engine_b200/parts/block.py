@@ -122,3 +122,20 @@ class PostNormMixerOnlyBlock(PostNormBlock):
     """The same arrangement for a layer without a feed-forward: one norm."""
 
     NORMS = ("mixer",)
+
+
+@register("block", "parallel")
+class ParallelBlock(Block):
+    """One norm, both sublayers read its output: ``x = x + (mixer(norm(x)) + feed_forward(norm(x)))``.  The three
+    terms (and the bias of the mixer's output projection) are added in 32-bit inside the next norm.  A layer may
+    have no feed-forward."""
+
+    capturable = True
+    NORMS = ("mixer",)
+    adds_output_bias = True
+
+    def forward(self, state: Residual, ctx: StepContext, cache: LayerCache) -> None:
+        h = self.mixer_norm.forward(state, ctx, ctx.dtype)
+        state.add(self.mixer.forward(h, ctx, cache), bias=self.mixer.output_bias)
+        if self.feed_forward is not None:
+            state.add_beside(self.feed_forward.forward(h, ctx))

@@ -76,11 +76,14 @@ class Linear:
 class GatedLinear:
     """``silu(x Wg^T) * (x Wu^T)`` from the row-concatenated weight ``[2 * inter, in]``; with a
     ``slope``, a ``limit`` or an ``offset`` the gated unit of :func:`ops.swiglu` with those constants
-    (as a kernel of its own behind the product: the fused epilogue is SwiGLU proper)."""
+    (as a kernel of its own behind the product: the fused epilogue is SwiGLU proper).  ``activation``
+    ``"gelu_tanh"`` gates with the tanh form of GELU instead of ``g * sigmoid(slope * g)``."""
 
-    def __init__(self, gate_up: torch.Tensor, slope: float = 1.0, limit: float | None = None, offset: float = 0.0):
-        self.slope, self.limit, self.offset = slope, limit, offset
-        self.plain = slope == 1.0 and limit is None and offset == 0.0
+    def __init__(
+        self, gate_up: torch.Tensor, slope: float = 1.0, limit: float | None = None, offset: float = 0.0, activation: str = "silu"
+    ):
+        self.slope, self.limit, self.offset, self.activation = slope, limit, offset, activation
+        self.plain = slope == 1.0 and limit is None and offset == 0.0 and activation == "silu"
         self.weight = gate_up
         self.inter = gate_up.shape[0] // 2
         self.in_features = gate_up.shape[1]
@@ -99,5 +102,5 @@ class GatedLinear:
             ops.gemm_tensor_core_swiglu(self.plan, x, act)
             return act
         both = self.linear.forward(x, ctx, name + ".gate_up")
-        ops.swiglu(both, act, self.slope, self.limit, self.offset)
+        ops.swiglu(both, act, self.slope, self.limit, self.offset, activation=self.activation)
         return act

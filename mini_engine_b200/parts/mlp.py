@@ -7,7 +7,8 @@ product's epilogue, so the ``[T, 2 * inter]`` intermediate never reaches memory.
 
 The gate has three constants for models whose gated unit differs: ``y = g * sigmoid(gate_slope * g) *
 (u + up_offset)`` with ``g = min(x Wg^T, limit)`` and ``u = clamp(x Wu^T, -limit, limit)`` when a
-``limit`` is given.  Slope 1, no limit and offset 0 are SwiGLU.
+``limit`` is given.  Slope 1, no limit and offset 0 are SwiGLU.  ``activation="gelu_tanh"`` gates with
+``0.5 g (1 + tanh(sqrt(2 / pi) (g + 0.044715 g^3)))`` in the place of ``g * sigmoid(gate_slope * g)``.
 """
 
 from __future__ import annotations
@@ -37,8 +38,9 @@ class GatedMLP(FeedForward):
         limit: float | None = None,
         up_offset: float = 0.0,
     ):
-        if activation != "silu":
-            raise ValueError(f"gated_mlp implements the 'silu' gate only, got {activation!r}")
+        if activation not in ("silu", "gelu_tanh"):
+            raise ValueError(f"gated_mlp gates with 'silu' or 'gelu_tanh', got {activation!r}")
+        self.activation = activation
         if limit is not None and not limit > 0:
             raise ValueError(f"the limit of the gated unit must be positive, got {limit}")
         self.hidden, self.inter = hidden_size, intermediate_size
@@ -60,7 +62,7 @@ class GatedMLP(FeedForward):
         n = self.names
         self.gate_up = GatedLinear(
             torch.cat((tensors[n["gate"]], tensors[n["up"]]), dim=0).contiguous(),
-            slope=self.gate_slope, limit=self.limit, offset=self.up_offset,
+            slope=self.gate_slope, limit=self.limit, offset=self.up_offset, activation=self.activation,
         )  # fmt: skip
         self.down = Linear(tensors[n["down"]])
 

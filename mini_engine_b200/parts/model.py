@@ -28,7 +28,7 @@ from mini_engine_b200.parts.base import (
 from mini_engine_b200.weights.loader import WeightSpec
 
 # Importing the built-in parts registers them.
-from mini_engine_b200.parts import attention, block, ends, linear_attention, mlp, moe, norms, parallel, recurrent, rotary  # noqa: F401,E402
+from mini_engine_b200.parts import attention, block, ends, latent_attention, linear_attention, mlp, moe, norms, parallel, recurrent, rotary  # noqa: F401,E402
 
 
 def build_block(spec: ModelSpec, index: int) -> Block:

@@ -1,10 +1,14 @@
-"""RMSNorm as a part.
+"""RMSNorm and layer norm as parts.
 
 ``y = w * (x * rsqrt(mean(x^2) + eps))`` with the statistics in 32-bit, eps inside the root
 (src/mini_engine/model.py:59-69 of YuvGev00/mini-engine).  The reference rounds the
 normalised value to the model dtype before the weight multiply; here the whole expression
 is evaluated in 32-bit and rounded once, which is at least as accurate.  The norm also
 performs the residual sum that precedes it (see :class:`~mini_engine_b200.parts.base.Residual`).
+
+``layernorm``: ``y = (x - mean(x)) / sqrt(var(x) + eps) * w + b`` with the variance as the mean of the
+squared deviations, weight and bias of the layer, all in 32-bit.  Its residual sum also takes the bias of
+an output projection and the output of a second sublayer that ran beside the first.
 """
 
 from __future__ import annotations
@@ -45,6 +49,8 @@ class RMSNorm(Norm):
     def forward(
         self, state: Residual, ctx: StepContext, out_dtype, rows=None, residual_scale: float = 1.0, keep_normed: bool = False
     ) -> torch.Tensor:
+        if state.pending_bias is not None or state.pending_more is not None:
+            raise ValueError("rmsnorm adds one pending output without a bias")
         count = state.x.shape[0] if rows is None else rows.shape[0]
         out = ctx.buffer("norm.out" if rows is None else "norm.rows", (count, self.dim), out_dtype)
         ops.add_rmsnorm(
@@ -53,4 +59,42 @@ class RMSNorm(Norm):
         if rows is None:
             state.clear()
             state.rounded = out if keep_normed else None  # with keep_normed, `out` is the new stream, rounded
+        return out
+
+
+@register("norm", "layernorm")
+class LayerNorm(Norm):
+    capturable = True
+
+    def __init__(self, prefix: str, hidden_size: int, *, name: str, eps: float, bias_name: str | None = None, dim: int | None = None):
+        """``name``: the weight's tensor; ``bias_name``: the bias's (by default ``name + ".b"``)."""
+        self.weight_name = prefix + name
+        self.bias_name = prefix + (bias_name if bias_name is not None else name + ".b")
+        self.dim = dim or hidden_size
+        self.eps = float(eps)
+        self.weight: torch.Tensor | None = None
+        self.bias: torch.Tensor | None = None
+
+    def weight_specs(self) -> list[WeightSpec]:
+        return [
+            WeightSpec(self.weight_name, (self.dim,), role="vector", init="ones_normal"),
+            WeightSpec(self.bias_name, (self.dim,), role="vector", init="small_normal"),
+        ]
+
+    def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
+        self.weight, self.bias = tensors[self.weight_name], tensors[self.bias_name]
+
+    def forward(
+        self, state: Residual, ctx: StepContext, out_dtype, rows=None, residual_scale: float = 1.0, keep_normed: bool = False
+    ) -> torch.Tensor:
+        if residual_scale != 1.0 or keep_normed or state.pending_scale is not None:
+            raise ValueError("layernorm stands in front of its sublayers: no factor on the stream, no scale, no write-back")
+        count = state.x.shape[0] if rows is None else rows.shape[0]
+        out = ctx.buffer("norm.out" if rows is None else "norm.rows", (count, self.dim), out_dtype)
+        ops.add_layernorm(
+            state.x, state.pending, self.weight, self.bias, self.eps, out, rows, state.pending_more, state.pending_bias
+        )
+        if rows is None:
+            state.clear()
+            state.rounded = None
         return out
