@@ -193,7 +193,7 @@ class GroupedQueryAttention(Mixer):
         if self.gates:
             specs.append(WeightSpec(n["gate"], (self.gates, self.hidden)))
         if self.learned_sink:
-            specs.append(WeightSpec(n["sink"], (self.heads,), role="vector", init="small_normal"))
+            specs.append(WeightSpec(n["sink"], (self.heads,), role="vector", init="wide_normal"))
         if self.has_output_bias:
             specs.append(WeightSpec(n["o_bias"], (self.hidden,), role="vector", init="small_normal"))
         if self.qk_norm_eps is not None:

@@ -84,6 +84,8 @@ def random_tensor(spec: WeightSpec, seed: int, dtype: torch.dtype, device="cpu",
         values = values + 1.0
     elif spec.init == "small_normal":
         values = values * NORM_STD
+    elif spec.init == "wide_normal":
+        pass  # N(0, 1): numbers that stand beside attention scores (a learned sink)
     elif spec.init == "positive":
         values = values.abs() * NORM_STD
         values = values + 0.05
