@@ -48,11 +48,24 @@ struct AttnParams {
     int page_shift;  // log2(page_size) when it is a power of two, else -1
     int tiles_per_cta;  // decode: consecutive 128-key tiles that one CTA walks
     int sink = 0;       // 1: the softmax has one more participant of score zero and no value (denominator + exp(-max))
-    const float* gate = nullptr;  // [tokens][heads] multiplier of each head's output, or null
+    const float* gate = nullptr;  // [tokens][heads][gate_width] multiplier of each head's output, or null
+    int gate_width = 1;           // 1: one multiplier per head; D: one per element
+    const float* slopes = nullptr;       // [heads] slope_h of a distance bias slope_h * (p - j) taken off the scaled scores, or null
+    const float* sink_values = nullptr;  // [heads] with sink: the silent participant's score (zero when null)
 };
 
 // What the silent participant adds to a denominator that is relative to `max_log2` (scores in the log2 domain).
-__device__ __forceinline__ float sink_term(const AttnParams& p, float max_log2) { return p.sink ? exp2f(-max_log2) : 0.0f; }
+__device__ __forceinline__ float sink_term(const AttnParams& p, float max_log2, int head) {
+    return p.sink ? exp2f((p.sink_values ? p.sink_values[head] * LOG2E : 0.0f) - max_log2) : 0.0f;
+}
+// The multiplier of element `col` of one (token, head)'s output.
+__device__ __forceinline__ float gate_of(const AttnParams& p, size_t token, int head, int col) {
+    if (!p.gate) return 1.0f;
+    const size_t at = token * p.heads + head;
+    return p.gate_width == 1 ? p.gate[at] : p.gate[at * p.gate_width + col];
+}
+// A head's slope in the log2 domain, in which the kernels keep their scores.
+__device__ __forceinline__ float slope_of(const AttnParams& p, int head) { return p.slopes ? p.slopes[head] * LOG2E : 0.0f; }
 
 // ------------------------------------------------------------------------ small helpers
 
@@ -157,11 +170,12 @@ __device__ __forceinline__ void accumulate_pv(float (&acc)[D / 8][4], const floa
 // Masks the scores of one tile, updates the running maximum and sum of the thread's two rows
 // (row `g` and row `g + 8` of the warp's 16) and turns the scores into probabilities.
 // `row_pos[i]` is the absolute position of row i's query; keys are visible in
-// [row_pos - window + 1, row_pos] (window <= 0: from 0).
+// [row_pos - window + 1, row_pos] (window <= 0: from 0).  `row_slope[i]` (log2 domain) times the distance to the
+// key is taken off row i's scaled scores.
 template <int D, int KEYS>
 __device__ __forceinline__ void softmax_step(float (&s)[KEYS / 8][4], float (&acc)[D / 8][4], float (&row_max)[2],
                                              float (&row_sum)[2], const int (&row_pos)[2], int first_key,
-                                             int window, float scale_log2, int lane) {
+                                             int window, float scale_log2, int lane, const float (&row_slope)[2]) {
     const int col0 = first_key + 2 * (lane & 3);
     float tile_max[2] = {-INFINITY, -INFINITY};
 #pragma unroll
@@ -171,7 +185,7 @@ __device__ __forceinline__ void softmax_step(float (&s)[KEYS / 8][4], float (&ac
             const int key = col0 + n * 8 + (i & 1);
             const int r = i >> 1;
             const bool visible = key <= row_pos[r] && (window <= 0 || key > row_pos[r] - window);
-            s[n][i] = visible ? s[n][i] * scale_log2 : -INFINITY;
+            s[n][i] = visible ? s[n][i] * scale_log2 - row_slope[r] * static_cast<float>(row_pos[r] - key) : -INFINITY;
             tile_max[r] = fmaxf(tile_max[r], s[n][i]);
         }
     float rescale[2], base[2];
@@ -263,6 +277,7 @@ __global__ void __launch_bounds__(ATTN_THREADS) attention_portions_kernel(AttnPa
         for (int i = 0; i < 4; ++i) acc[n][i] = 0.0f;
     float row_max[2] = {-INFINITY, -INFINITY}, row_sum[2] = {0.0f, 0.0f};
     const int row_pos[2] = {pos0 + warp * 16 + (lane >> 2), pos0 + warp * 16 + (lane >> 2) + 8};
+    const float row_slope[2] = {slope_of(p, head), slope_of(p, head)};
 
     for (int tile = first_tile; tile <= last_tile; ++tile) {
         const int s = (tile - first_tile) & 1;
@@ -284,7 +299,7 @@ __global__ void __launch_bounds__(ATTN_THREADS) attention_portions_kernel(AttnPa
         const __nv_bfloat16* k_tile = kv_tiles + s * 2 * BLOCK_KEYS * D;
         float scores[BLOCK_KEYS / 8][4];
         scores_tile<D, BLOCK_KEYS>(scores, q_frag, k_tile, lane);
-        softmax_step<D, BLOCK_KEYS>(scores, acc, row_max, row_sum, row_pos, tile * BLOCK_KEYS, p.window, p.scale_log2, lane);
+        softmax_step<D, BLOCK_KEYS>(scores, acc, row_max, row_sum, row_pos, tile * BLOCK_KEYS, p.window, p.scale_log2, lane, row_slope);
         accumulate_pv<D, BLOCK_KEYS>(acc, scores, k_tile + BLOCK_KEYS * D, lane);
         __syncthreads();  // the next iteration's prefetch overwrites the other stage's reader
     }
@@ -298,13 +313,16 @@ __global__ void __launch_bounds__(ATTN_THREADS) attention_portions_kernel(AttnPa
     for (int r = 0; r < 2; ++r) {
         const int row = warp * 16 + (lane >> 2) + r * 8;
         if (row >= rows_valid) continue;
-        float inv = 1.0f / (row_sum[r] + sink_term(p, row_max[r]));
-        if (p.gate) inv *= p.gate[static_cast<size_t>(token0 + q_block * BLOCK_M + row) * p.heads + head];
-        __nv_bfloat16* dst = p.out + (static_cast<size_t>(token0 + q_block * BLOCK_M + row) * p.heads + head) * D;
+        const float inv = 1.0f / (row_sum[r] + sink_term(p, row_max[r], head));
+        const size_t token = static_cast<size_t>(token0 + q_block * BLOCK_M + row);
+        __nv_bfloat16* dst = p.out + (token * p.heads + head) * D;
+        const float whole = p.gate_width == 1 ? inv * gate_of(p, token, head, 0) : inv;
 #pragma unroll
         for (int n = 0; n < D / 8; ++n) {
             const int col = n * 8 + 2 * (lane & 3);
-            *reinterpret_cast<uint32_t*>(dst + col) = pack_bf16(acc[n][r * 2] * inv, acc[n][r * 2 + 1] * inv);
+            float a = acc[n][r * 2] * whole, b = acc[n][r * 2 + 1] * whole;
+            if (p.gate_width != 1) a *= gate_of(p, token, head, col), b *= gate_of(p, token, head, col + 1);
+            *reinterpret_cast<uint32_t*>(dst + col) = pack_bf16(a, b);
         }
     }
 }
@@ -399,6 +417,8 @@ __global__ void __launch_bounds__(ATTN_THREADS, 3) attention_decode_kernel(AttnP
     float row_max[2] = {-INFINITY, -INFINITY}, row_sum[2] = {0.0f, 0.0f};
     uint32_t q_frag[D / 16][4];
     const int row_pos[2] = {position, position};
+    const int row_head[2] = {kv_head * group + min(lane >> 2, group - 1), kv_head * group + min((lane >> 2) + 8, group - 1)};
+    const float row_slope[2] = {slope_of(p, row_head[0]), slope_of(p, row_head[1])};
 
 #pragma unroll 1
     for (int t = 0; t < tiles; ++t) {
@@ -418,7 +438,7 @@ __global__ void __launch_bounds__(ATTN_THREADS, 3) attention_decode_kernel(AttnP
         const int first_key = cta_start + t * DECODE_CHUNK + warp * KEYS;
         float scores[KEYS / 8][4];
         scores_tile<D, KEYS>(scores, q_frag, k_tile, lane);
-        softmax_step<D, KEYS>(scores, acc, row_max, row_sum, row_pos, first_key, p.window, p.scale_log2, lane);
+        softmax_step<D, KEYS>(scores, acc, row_max, row_sum, row_pos, first_key, p.window, p.scale_log2, lane, row_slope);
         __syncwarp();  // every lane has read the keys: the next tile's keys may overwrite them
         if (more) issue(k_tile, p.k_pages, offset_next);
         cp_async_commit();
@@ -550,11 +570,14 @@ __device__ __forceinline__ void merge_head(const AttnParams& p, int entry, int h
     }
     const int token = p.cu_tokens[entry];
     __nv_bfloat16* dst = p.out + (static_cast<size_t>(token) * p.heads + head) * D + lane * PER_LANE;
-    float inv = 1.0f / (denom + sink_term(p, total_max));
-    if (p.gate) inv *= p.gate[static_cast<size_t>(token) * p.heads + head];
+    float inv = 1.0f / (denom + sink_term(p, total_max, head));
+    if (p.gate_width == 1) inv *= gate_of(p, token, head, 0);
 #pragma unroll
-    for (int i = 0; i < PER_LANE; i += 2)
-        *reinterpret_cast<uint32_t*>(dst + i) = pack_bf16(value[i] * inv, value[i + 1] * inv);
+    for (int i = 0; i < PER_LANE; i += 2) {
+        float a = value[i] * inv, b = value[i + 1] * inv;
+        if (p.gate_width != 1) a *= gate_of(p, token, head, lane * PER_LANE + i), b *= gate_of(p, token, head, lane * PER_LANE + i + 1);
+        *reinterpret_cast<uint32_t*>(dst + i) = pack_bf16(a, b);
+    }
 }
 
 // One warp per (entry, head), for callers that give the decode kernel no arrival counters.
@@ -728,6 +751,8 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __g
 #pragma unroll
         for (int j = 0; j < 4; ++j) acc[i][j] = 0.0f;
     float row_max[2] = {-INFINITY, -INFINITY}, row_sum[2] = {0.0f, 0.0f};  // of heads 2 (lane % 4) and + 1
+    const float head_slope[2] = {slope_of(p, kv_head * group + min(2 * (lane & 3), group - 1)),
+                                 slope_of(p, kv_head * group + min(2 * (lane & 3) + 1, group - 1))};
     uint32_t phase = 0;
     bool failed = false;
 
@@ -763,8 +788,8 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __g
             float prob[4];
 #pragma unroll
             for (int j = 0; j < 2; ++j) {
-                const float a = seen0 ? s[j] * p.scale_log2 : -INFINITY;
-                const float b = seen1 ? s[j + 2] * p.scale_log2 : -INFINITY;
+                const float a = seen0 ? s[j] * p.scale_log2 - head_slope[j] * static_cast<float>(position - key0) : -INFINITY;
+                const float b = seen1 ? s[j + 2] * p.scale_log2 - head_slope[j] * static_cast<float>(position - key0 - 8) : -INFINITY;
                 float tile_max = fmaxf(a, b);
                 tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, 4));
                 tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, 8));
@@ -865,8 +890,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __g
         if (!direct)
             p.partials[((static_cast<size_t>(entry) * p.heads + head) * p.max_splits + split) * STRIDE + col] = value;
         else if (col < D) {
-            float result = value / (denom + sink_term(p, total_max));
-            if (p.gate) result *= p.gate[static_cast<size_t>(token) * p.heads + head];
+            const float result = value / (denom + sink_term(p, total_max, head)) * gate_of(p, token, head, col);
             p.out[(static_cast<size_t>(token) * p.heads + head) * D + col] = __float2bfloat16(result);
         }
     }
@@ -960,13 +984,14 @@ ME_EXPORT int me_attention_portions_bf16(const void* q, const void* k_pages, con
                                          const int* cu_tokens, const int* context_lens, void* out, float scale,
                                          int entries, int max_new_tokens, int heads, int kv_heads, int head_dim,
                                          int page_size, int table_width, int window, const int* entry_ids,
-                                         int sink, const float* gate, cudaStream_t stream) {
+                                         int sink, const float* gate, int gate_width, const float* slopes,
+                                         const float* sink_values, cudaStream_t stream) {
     if (entries <= 0) return 0;
     if (!sizes_ok(head_dim, heads, kv_heads)) return ME_ERR_UNSUPPORTED;
     AttnParams p{static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(k_pages),
                  static_cast<const __nv_bfloat16*>(v_pages), block_table, cu_tokens, context_lens,
                  static_cast<__nv_bfloat16*>(out), nullptr, nullptr, entry_ids, scale * LOG2E, heads, kv_heads,
-                 page_size, table_width, window, 0, shift_of(page_size), 1, sink, gate};
+                 page_size, table_width, window, 0, shift_of(page_size), 1, sink, gate, gate_width, slopes, sink_values};
     return head_dim == 128 ? launch_portions<128>(p, entries, max_new_tokens, stream)
                            : launch_portions<64>(p, entries, max_new_tokens, stream);
 }
@@ -982,14 +1007,16 @@ ME_EXPORT int me_attention_decode_bf16_tiled(const void* q, const void* k_pages,
                                              void* out, float* partials, int* counters, float scale, int entries, int max_splits,
                                              int tiles_per_cta, int heads, int kv_heads, int head_dim, int page_size,
                                              int table_width, int window, const int* entry_ids, int sink,
-                                             const float* gate, cudaStream_t stream) {
+                                             const float* gate, int gate_width, const float* slopes,
+                                             const float* sink_values, cudaStream_t stream) {
     if (entries <= 0) return 0;
     if (!sizes_ok(head_dim, heads, kv_heads) || heads / kv_heads > 16 || max_splits < 1) return ME_ERR_UNSUPPORTED;
     if (tiles_per_cta < 1 || tiles_per_cta > MAX_DECODE_TILES) return ME_ERR_ARGUMENT;
     AttnParams p{static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(k_pages),
                  static_cast<const __nv_bfloat16*>(v_pages), block_table, cu_tokens, context_lens,
                  static_cast<__nv_bfloat16*>(out), partials, counters, entry_ids, scale * LOG2E, heads, kv_heads,
-                 page_size, table_width, window, max_splits, shift_of(page_size), tiles_per_cta, sink, gate};
+                 page_size, table_width, window, max_splits, shift_of(page_size), tiles_per_cta, sink, gate, gate_width,
+                 slopes, sink_values};
     return head_dim == 128 ? launch_decode<128>(p, entries, stream) : launch_decode<64>(p, entries, stream);
 }
 
@@ -1004,7 +1031,8 @@ ME_EXPORT int me_attention_decode_bf16_tma(const void* k_map, const void* v_map,
                                            const int* cu_tokens, const int* context_lens, void* out, float* partials,
                                            int* counters, float scale, int entries, int splits, int warps, int heads,
                                            int kv_heads, int head_dim, int page_size, int table_width, int window,
-                                           const int* entry_ids, int sink, const float* gate, cudaStream_t stream) {
+                                           const int* entry_ids, int sink, const float* gate, int gate_width,
+                                           const float* slopes, const float* sink_values, cudaStream_t stream) {
     if (entries <= 0) return 0;
     if (!sizes_ok(head_dim, heads, kv_heads) || heads / kv_heads > 8) return ME_ERR_UNSUPPORTED;
     if (shift_of(page_size) < 3) return ME_ERR_UNSUPPORTED;
@@ -1012,7 +1040,7 @@ ME_EXPORT int me_attention_decode_bf16_tma(const void* k_map, const void* v_map,
     if (warps != 8 && warps != 6) return ME_ERR_ARGUMENT;
     AttnParams p{static_cast<const __nv_bfloat16*>(q), nullptr, nullptr, block_table, cu_tokens, context_lens,
                  static_cast<__nv_bfloat16*>(out), partials, counters, entry_ids, scale * LOG2E, heads, kv_heads,
-                 page_size, table_width, window, splits, shift_of(page_size), 0, sink, gate};
+                 page_size, table_width, window, splits, shift_of(page_size), 0, sink, gate, gate_width, slopes, sink_values};
     CUtensorMap maps[2];
     memcpy(&maps[0], k_map, sizeof(CUtensorMap));
     memcpy(&maps[1], v_map, sizeof(CUtensorMap));
@@ -1040,7 +1068,7 @@ ME_EXPORT int me_attention_decode_bf16(const void* q, const void* k_pages, const
                                        int page_size, int table_width, int window, cudaStream_t stream) {
     return me_attention_decode_bf16_tiled(q, k_pages, v_pages, block_table, cu_tokens, context_lens, out, partials,
                                           nullptr, scale, entries, max_splits, 1, heads, kv_heads, head_dim, page_size,
-                                          table_width, window, nullptr, 0, nullptr, stream);
+                                          table_width, window, nullptr, 0, nullptr, 1, nullptr, nullptr, stream);
 }
 
 // ------------------------------------------------- decode attention without allocation

@@ -112,11 +112,11 @@ def _library():
         import ctypes
 
         lib = load_library("attention_bf16")
-        lib.me_attention_portions_bf16.argtypes = [c_void_p] * 7 + [c_float] + [c_int] * 8 + [c_void_p, c_int, c_void_p, c_void_p]
+        lib.me_attention_portions_bf16.argtypes = [c_void_p] * 7 + [c_float] + [c_int] * 8 + [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p]
         lib.me_attention_portions_bf16.restype = c_int
-        lib.me_attention_decode_bf16_tiled.argtypes = [c_void_p] * 9 + [c_float] + [c_int] * 9 + [c_void_p, c_int, c_void_p, c_void_p]
+        lib.me_attention_decode_bf16_tiled.argtypes = [c_void_p] * 9 + [c_float] + [c_int] * 9 + [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p]
         lib.me_attention_decode_bf16_tiled.restype = c_int
-        lib.me_attention_decode_bf16_tma.argtypes = [c_void_p] * 9 + [c_float] + [c_int] * 9 + [c_void_p, c_int, c_void_p, c_void_p]
+        lib.me_attention_decode_bf16_tma.argtypes = [c_void_p] * 9 + [c_float] + [c_int] * 9 + [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p]
         lib.me_attention_decode_bf16_tma.restype = c_int
         lib.me_attention_bf16_take_error.argtypes = [ctypes.POINTER(c_int)]
         lib.me_attention_bf16_take_error.restype = c_int
@@ -187,23 +187,34 @@ def decode_splits(max_context_len: int, tiles_per_cta: int = 1) -> int:
 
 def paged_attention(q, k_pages, v_pages, block_table, ctx, out, heads, kv_heads, head_dim, scale, window,
                     decode_warps: int | None = None, decode_splits_per_pair: int | None = None, sink: bool = False,
-                    gate: torch.Tensor | None = None) -> None:
+                    gate: torch.Tensor | None = None, slopes: torch.Tensor | None = None,
+                    sink_values: torch.Tensor | None = None) -> None:
     """Attention of the batch's new tokens.  Entries that bring one token take the split decode
     kernel, the others a portions kernel; a step that holds both kinds is two launches, each over
     its own list of entries.  ``decode_warps`` (6 or 8) and ``decode_splits_per_pair`` pin the form
     of the TMA decode kernel that the rules above would otherwise choose from the batch: the kernel
     tests run every case in both forms, and the kernel bench times one form against the other.
-    ``sink``: the softmax has one more participant of score zero and no value; ``gate`` (float32 ``[T, heads]``):
-    a multiplier on every head's output.  Both are known to the mma.sync kernels, so with either of them a
-    prompt portion takes the portions kernel where it would otherwise take the tcgen05 kernel."""
+    ``sink``: the softmax has one more participant of score zero and no value, or of the learned score
+    ``sink_values[h]`` (float32 ``[heads]``); ``gate`` (float32 ``[T, heads]`` or ``[T, heads * head_dim]``): a
+    multiplier on every head's output, or on every element; ``slopes`` (float32 ``[heads]``): ``slopes[h] * (p - j)``
+    is taken off the scaled score of query ``p`` and key ``j``.  All are known to the mma.sync kernels, so with any of
+    them a prompt portion takes the portions kernel where it would otherwise take the tcgen05 kernel."""
     for name, t in (("q", q), ("out", out), ("k_pages", k_pages), ("v_pages", v_pages)):
         if t.dtype != torch.bfloat16 or not t.is_contiguous():
             raise ops.KernelError(f"{name} must be contiguous bfloat16")
     if block_table.dtype != torch.int32 or not block_table.is_contiguous():
         raise ops.KernelError("block_table must be contiguous int32")
-    if gate is not None and (gate.dtype != torch.float32 or not gate.is_contiguous() or gate.shape != (q.shape[0], heads)):
-        raise ops.KernelError("gate must be contiguous float32 [tokens, heads]")
-    sink_flag, gate_ptr = (1 if sink else 0), (None if gate is None else gate.data_ptr())
+    gate_width = 1
+    if gate is not None:
+        if gate.dtype != torch.float32 or not gate.is_contiguous() or gate.shape not in ((q.shape[0], heads), (q.shape[0], heads * head_dim)):
+            raise ops.KernelError("gate must be contiguous float32 [tokens, heads] or [tokens, heads * head_dim]")
+        gate_width = gate.shape[1] // heads
+    for name, vector in (("slopes", slopes), ("sink_values", sink_values)):
+        if vector is not None and (vector.dtype != torch.float32 or not vector.is_contiguous() or vector.shape != (heads,)):
+            raise ops.KernelError(f"{name} must be contiguous float32 [heads]")
+    sink_flag, gate_ptr = (1 if (sink or sink_values is not None) else 0), (None if gate is None else gate.data_ptr())
+    options = (sink_flag, gate_ptr, gate_width, None if slopes is None else slopes.data_ptr(),
+               None if sink_values is None else sink_values.data_ptr())  # fmt: skip
     stream = _ops_stream()
     page_size, width = k_pages.shape[2], block_table.shape[1]
     common = (q.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), block_table.data_ptr(), ctx.cu_tokens.data_ptr(),
@@ -232,7 +243,7 @@ def paged_attention(q, k_pages, v_pages, block_table, ctx, out, heads, kv_heads,
             rows = min(page_size, TMA_DECODE_KEYS)
             code = _library().me_attention_decode_bf16_tma(
                 _page_map(k_pages, rows), _page_map(v_pages, rows), common[0], *common[3:], partials, counters, scale,
-                entries, splits, warps, heads, kv_heads, head_dim, page_size, width, window, ids_ptr, sink_flag, gate_ptr, stream,
+                entries, splits, warps, heads, kv_heads, head_dim, page_size, width, window, ids_ptr, *options, stream,
             )  # fmt: skip
             ops._check(code, "attention_decode_bf16_tma")
         elif kind == "decode":
@@ -242,10 +253,10 @@ def paged_attention(q, k_pages, v_pages, block_table, ctx, out, heads, kv_heads,
             counters = ctx.workspace.zeroed("attn.counters", ctx.num_entries * kv_heads)
             code = _library().me_attention_decode_bf16_tiled(
                 *common, partials.data_ptr(), counters.data_ptr(), scale, entries, splits, tiles, heads, kv_heads,
-                head_dim, page_size, width, window, ids_ptr, sink_flag, gate_ptr, stream,
+                head_dim, page_size, width, window, ids_ptr, *options, stream,
             )  # fmt: skip
             ops._check(code, "attention_decode_bf16")
-        elif not sink and gate is None and tensor_memory_kernel_takes(head_dim, page_size, window, longest):
+        elif not sink_flag and gate is None and slopes is None and tensor_memory_kernel_takes(head_dim, page_size, window, longest):
             code = _tc_library().me_attention_tcgen05(
                 _query_map(q), _page_map(k_pages), _page_map(v_pages), *common[3:], scale, entries, longest, heads,
                 kv_heads, head_dim, page_size, width, ids_ptr, stream,
@@ -253,7 +264,7 @@ def paged_attention(q, k_pages, v_pages, block_table, ctx, out, heads, kv_heads,
             ops._check(code, "attention_tcgen05")
         else:
             code = _library().me_attention_portions_bf16(
-                *common, scale, entries, longest, heads, kv_heads, head_dim, page_size, width, window, ids_ptr, sink_flag, gate_ptr,
+                *common, scale, entries, longest, heads, kv_heads, head_dim, page_size, width, window, ids_ptr, *options,
                 stream,
             )
             ops._check(code, "attention_portions_bf16")

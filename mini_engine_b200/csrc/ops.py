@@ -503,14 +503,13 @@ def paged_attention(
     """Causal attention of the batch's new tokens over their requests' cached keys (the new
     tokens' own keys are already in the cache).  Chooses the kernel by dtype and sizes.  ``value_dim``,
     ``sink``, ``gate``, ``slopes`` and ``sink_values`` as in :func:`paged_attention_generic`; value heads of another
-    width than the key heads, values inside the key rows (``v_pages=None``), a gate per element, a distance bias
-    and learned sinks take that kernel."""
-    plain = slopes is None and sink_values is None and v_pages is not None and (gate is None or gate.shape[1] == heads)
-    if plain and q.dtype == torch.bfloat16 and value_dim in (None, head_dim):
+    width than the key heads and values inside the key rows (``v_pages=None``) take that kernel."""
+    if v_pages is not None and q.dtype == torch.bfloat16 and value_dim in (None, head_dim):
         if attention_bf16.supports(head_dim, heads, kv_heads):
             attention_bf16.paged_attention(
-                q, k_pages, v_pages, block_table, ctx, out, heads, kv_heads, head_dim, scale, window, sink=sink, gate=gate
-            )
+                q, k_pages, v_pages, block_table, ctx, out, heads, kv_heads, head_dim, scale, window, sink=sink, gate=gate,
+                slopes=slopes, sink_values=sink_values,
+            )  # fmt: skip
             return
     paged_attention_generic(
         q, k_pages, v_pages, block_table, ctx.entry_of_token, ctx.positions, out, heads, kv_heads, head_dim,

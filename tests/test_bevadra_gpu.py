@@ -483,6 +483,59 @@ def test_a_key_that_stands_out_at_the_windows_edge(window, offset, dtype_name, k
         assert torch.allclose(got, want[positions], atol=tolerance * 100.0, rtol=tolerance)
 
 
+@pytest.mark.parametrize("head_dim", [64, 128])
+@pytest.mark.parametrize("heads,kv_heads,page", [(4, 2, 8), (8, 1, 16), (12, 1, 16), (4, 4, 4)])
+@pytest.mark.parametrize("news", [[1, 1, 1, 1], [90, 5, 130, 2], [1, 40, 1, 7]])
+@pytest.mark.parametrize("window", [0, 70])
+def test_tensor_core_attention_with_bias_sinks_and_element_gates(head_dim, heads, kv_heads, page, news, window):
+    """The bfloat16 kernels on tensor cores (prompt portions; decode by TMA for groups up to 8 and pages from 8
+    tokens, else the tiled one; mixed steps) with the distance bias, learned sinks and a gate per element, against
+    float64."""
+    from test_kernels_gpu import fake_context
+
+    from mini_engine_b200.csrc import attention_bf16, ops
+
+    g = torch.Generator().manual_seed(head_dim + heads + page + len(news) + window)
+    lengths = [400, 90, 130, 300]
+    total_pages = sum(-(-n // page) for n in lengths) + 3
+    order = torch.randperm(total_pages, generator=g).tolist()
+    k_pages = torch.randn(total_pages, kv_heads, page, head_dim, generator=g).to(torch.bfloat16)
+    v_pages = torch.randn(total_pages, kv_heads, page, head_dim, generator=g).to(torch.bfloat16)
+    table = torch.full((len(lengths), max(-(-n // page) for n in lengths) + 1), -1, dtype=torch.int32)
+    slopes = 20.0 * slopes_of(heads)  # steep enough that the nearest keys carry the weight of the first heads
+    sink = 3.0 * torch.randn(heads, generator=g)
+    q_rows, want_rows, gate_rows, entry_of, positions = [], [], [], [], []
+    for b, (n, new) in enumerate(zip(lengths, news)):
+        q = (0.5 * torch.randn(n, heads, head_dim, generator=g)).to(torch.bfloat16)
+        k = torch.randn(n, kv_heads, head_dim, generator=g).to(torch.bfloat16)
+        v = torch.randn(n, kv_heads, head_dim, generator=g).to(torch.bfloat16)
+        gate = torch.rand(n, heads * head_dim, generator=g)
+        for i in range(-(-n // page)):
+            table[b, i] = order.pop()
+        for p in range(n):
+            k_pages[table[b, p // page], :, p % page] = k[p]
+            v_pages[table[b, p // page], :, p % page] = v[p]
+        want = plain_biased_attention(q.double(), k.double(), v.double(), head_dim**-0.5, window or None, slopes, sink, gate)
+        q_rows.append(q[n - new :]), want_rows.append(want[n - new :]), gate_rows.append(gate[n - new :])
+        entry_of += [b] * new
+        positions += list(range(n - new, n))
+    data = dict(new_counts=news, lengths=lengths, entry_of=torch.tensor(entry_of, dtype=torch.int32).cuda(),
+                positions=torch.tensor(positions, dtype=torch.int32).cuda())  # fmt: skip
+    q_all = torch.cat(q_rows).reshape(-1, heads * head_dim).contiguous().cuda()
+    want = torch.cat(want_rows).reshape(-1, heads * head_dim).float()
+    out = torch.full_like(q_all, float("nan"))
+    assert attention_bf16.supports(head_dim, heads, kv_heads)
+    ops.paged_attention(
+        q=q_all, k_pages=k_pages.cuda(), v_pages=v_pages.cuda(), block_table=table.cuda(), ctx=fake_context(data), out=out,
+        heads=heads, kv_heads=kv_heads, head_dim=head_dim, scale=head_dim**-0.5, window=window,
+        gate=torch.cat(gate_rows).contiguous().cuda(), slopes=slopes.cuda(), sink_values=sink.cuda(),
+    )  # fmt: skip
+    torch.cuda.synchronize()
+    assert attention_bf16.take_error() == 0
+    error = float((out.float().cpu() - want).abs().max()) / float(want.abs().max())
+    assert error < 2e-2, f"relative error {error:.3g}"
+
+
 # ---------------------------------------------------------------------- mechanisms alone: the latent layer
 
 
