@@ -1,7 +1,7 @@
-"""Prefill and decode throughput of another design (Pimezen, Molotar) beside Qwen3 dense at equal layer sizes.
+"""Prefill and decode throughput of another design (Pimezen, Molotar, Bevadra) beside Qwen3 dense at equal layer sizes.
 
-    python -m mini_engine_b200.cli.design_bench [--design pimezen|molotar] [--sizes 1b,8b] [--steps K] [--warmup W]
-    (or: bench.py --design pimezen|molotar)
+    python -m mini_engine_b200.cli.design_bench [--design pimezen|molotar|bevadra] [--sizes 1b,8b] [--steps K] [--warmup W]
+    (or: bench.py --design pimezen|molotar|bevadra)
 
 For each size both models get the same width, feed-forward width, head counts, head size, layer count
 and vocabulary, seeded random bfloat16 weights, and the same two workloads: one prompt of 2,048 tokens
@@ -17,6 +17,11 @@ and values; its attention has Qwen3's head counts and head size, a window of 1,0
 rotated; its recurrence is as wide as the model with blocks of 128 channels and four taps; its feed-forward has 8
 units in 4 groups of which 2 are kept, a token uses 2 units, and a unit is half as wide as Qwen3's feed-forward, so
 that a token uses as many feed-forward weights as in Qwen3 while the layer holds four times as many.
+
+Bevadra gets four layers in the order attention, latent attention, attention that reads the first layer's keys and
+values, latent attention; its attention has Qwen3's head counts and head size and a window of 1,024 tokens; its latent
+attention has as many heads with 128 plain and 64 rotated query/key elements, values of 128, a key/value latent of 512
+and a query latent of three eighths of the width, and the same window; its feed-forward is as wide as Qwen3's.
 """
 
 from __future__ import annotations
@@ -39,7 +44,8 @@ SIZES = {
 TIMED = ("biased_attention", "mixed_attention", "gla_scan", "gla_finish", "branch_sum", "paged_attention", "qk_norm_rope_store",
          "add_rmsnorm", "swiglu", "gemm_tensor_core", "gemm_tensor_core_swiglu", "embedding", "rglru", "route",
          "qk_wide_norm_rope_store", "pair_embedding", "round_rows", "gemm_tensor_core_grouped", "sort_by_unit", "gather_rows",
-         "combine_rows")  # fmt: skip
+         "combine_rows", "add_layernorm", "latent_down_finish", "head_product", "logits_finish")  # fmt: skip
+LATENT_RANK, LATENT_ROT = 512, 64
 UNITS, UNITS_USED, UNIT_GROUPS, UNIT_GROUPS_KEPT = 8, 2, 4, 2
 RECURRENCE_BLOCK, RECURRENCE_TAPS = 128, 4
 
@@ -61,6 +67,20 @@ def molotar_config(size: dict):
         "embedding": {"scale": size["width"] ** 0.5, "bigram": {"buckets": 65521, "mul_prev": 31, "mul_cur": 7}},
         "layers": layers,
     })  # fmt: skip
+
+
+def bevadra_config(size: dict):
+    from mini_engine_b200.config import BevadraConfig
+
+    d, h = size["head_dim"], size["heads"]
+    attention = {"heads": h, "kv_heads": size["kv_heads"], "dim": d, "vdim": d, "scale": d**-0.5, "mask": {"size": WINDOW}}
+    latent = {"heads": h, "dim": d, "rot_dim": LATENT_ROT, "vdim": d, "kv_rank": LATENT_RANK, "q_rank": 3 * size["width"] // 8,
+              "scale": (d + LATENT_ROT) ** -0.5, "mask": {"size": WINDOW}, "rot": {"dims": LATENT_ROT, "base": 1e4}}  # fmt: skip
+    mlp = {"kind": "dense", "ff": size["ff"]}
+    pattern = [("attention", attention), ("latent_attention", latent), ("attention", {**attention, "kv_from": 0}), ("latent_attention", latent)]
+    layers = [{"type": kind, "mixer": mixer, "mlp": mlp} for kind, mixer in (pattern * size["layers"])[: size["layers"]]]
+    return BevadraConfig.from_dict({"architecture": "Bevadra", "vocab": size["vocab"], "width": size["width"], "norm": {"eps": 1e-5},
+                                    "logit_softcap": 30.0, "layers": layers})  # fmt: skip
 
 
 def configs(size: dict, design: str = "pimezen"):
@@ -85,6 +105,8 @@ def configs(size: dict, design: str = "pimezen"):
                                        "norm": {"eps": 1e-6}, "layers": [layer] * size["layers"]})  # fmt: skip
     if design == "molotar":
         return {"molotar": molotar_config(size), "qwen3": qwen}
+    if design == "bevadra":
+        return {"bevadra": bevadra_config(size), "qwen3": qwen}
     return {"pimezen": pimezen, "qwen3": qwen}
 
 
@@ -102,6 +124,8 @@ class KernelTimes:
         self.saved = {name: getattr(ops, name) for name in TIMED}
         for name, function in self.saved.items():
             def timed(*args, _name=name, _function=function, **kwargs):
+                if _name == "paged_attention" and kwargs.get("v_pages", 0) is None:
+                    _name = "latent_attention"  # the same entry point over a cache of latent rows
                 start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 start.record()
                 result = _function(*args, **kwargs)
@@ -148,7 +172,7 @@ def rooflines(design: str, size: dict, peaks: dict) -> dict:
     def bound(name, nbytes, nflops):
         out[name] = {"bytes": nbytes, "flops": nflops, "roofline_us": max(nbytes / bw, nflops / flops) * 1e6}
 
-    window = WINDOW if design in ("pimezen", "molotar") else None
+    window = WINDOW if design in ("pimezen", "molotar", "bevadra") else None
     keep = KEEP_FIRST if design == "pimezen" else 0
     seen_prompt = visible_sum(0, PROMPT, window, keep)
     seen_decode = BATCH * visible_sum(CONTEXT, CONTEXT + 1, window, keep)
@@ -184,6 +208,29 @@ def rooflines(design: str, size: dict, peaks: dict) -> dict:
         for name in ("prompt.paged_attention", "decode.paged_attention", "prompt.rglru", "decode.rglru"):
             out[name] = {key: value * 0.5 for key, value in out[name].items()}
         # (the products' record counts the activation kernel of the masked form as well: Qwen3's runs in its product's epilogue)
+    elif design == "bevadra":
+        rank, rot, q_rank = LATENT_RANK, LATENT_ROT, 3 * width // 8
+        key = rank + rot
+        # attention: the gates of every element are read as well (32-bit)
+        for phase, tokens in (("prompt", PROMPT), ("decode", BATCH)):
+            out[f"{phase}.paged_attention"]["bytes"] += tokens * h * d * 4
+        for phase, tokens, seen in (("prompt", PROMPT, seen_prompt), ("decode", BATCH, seen_decode)):
+            rows = tokens if phase == "prompt" else seen  # cached rows that the step reads at least once
+            bound(f"{phase}.latent_attention", (rows * key + tokens * h * (key + rank)) * 2, seen * h * 2 * (key + rank))
+            # the two per-head products: queries into the latent's space, averaged latents into values
+            bound(f"{phase}.head_product", (2 * h * d * rank + tokens * h * (2 * d + rot + key + rank)) * 2, 2 * tokens * 2 * h * d * rank)
+        mixers = [width * (2 * h * d + 2 * g * d) + h * d * width, width * (q_rank + key + h) + q_rank * h * (d + rot) + h * d * width,
+                  width * 2 * h * d + h * d * width, width * (q_rank + key + h) + q_rank * h * (d + rot) + h * d * width]  # fmt: skip
+        mixer = sum(mixers) / len(mixers)
+        dense = 3 * width * ff
+        for phase, tokens in (("prompt", PROMPT), ("decode", BATCH)):
+            nbytes, nflops = (mixer + dense) * 2, 2 * tokens * (mixer + dense)
+            out[f"{phase}.products"] = {"bytes": nbytes, "flops": nflops, "roofline_us": max(nbytes / bw, nflops / flops) * 1e6,
+                                        "kernels": ("gemm_tensor_core", "gemm_tensor_core_swiglu", "swiglu")}  # fmt: skip
+        # kernel times are averaged over all layers, of which half have an attention and half a latent attention
+        for name in [n for n in out if n.split(".")[1] in ("paged_attention", "latent_attention", "head_product")]:
+            nbytes, nflops = out[name]["bytes"] * 0.5, out[name]["flops"] * 0.5
+            out[name] = {"bytes": nbytes, "flops": nflops, "roofline_us": max(nbytes / bw, nflops / flops) * 1e6}
     elif design == "qwen3":
         mixer = width * (h * d + 2 * g * d) + h * d * width
         dense = 3 * width * ff
@@ -330,7 +377,7 @@ def run(sizes: list[str], steps: int, warmup: int, design: str = "pimezen") -> d
 
 def main(argv=None) -> int:
     parser = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
-    parser.add_argument("--design", choices=["pimezen", "molotar"], default="pimezen")
+    parser.add_argument("--design", choices=["pimezen", "molotar", "bevadra"], default="pimezen")
     parser.add_argument("--sizes", default="1b,8b")
     parser.add_argument("--steps", type=int, default=32)
     parser.add_argument("--warmup", type=int, default=5)
