@@ -34,6 +34,7 @@ LIBRARIES = {
     "attention_generic": "attention_generic.cu",
     "attention_biased": "attention_biased.cu",
     "latent_attention": "latent_attention.cu",
+    "latent_attention_bf16": "latent_attention_bf16.cu",
     "linear_attention": "linear_attention.cu",
     "recurrent": "recurrent.cu",
     "routing": "routing.cu",

@@ -19,7 +19,7 @@
 // handed over with mbarriers: full[s] (TMA bytes arrived), empty[s] (tcgen05.commit: the MMAs
 // that read stage s retired), accum (all MMAs retired).
 //
-// DUAL mode computes silu(x Wg^T) * (x Wu^T) (src/mini_engine/model.py:130): Wg and Wu tiles
+// DUAL mode computes silu(x Wg^T) * (x Wu^T) (or, `act_gelu`, the tanh form of GELU as the gate) (src/mini_engine/model.py:130): Wg and Wu tiles
 // of the same 128 output features are loaded side by side, accumulate into two column ranges
 // of tensor memory, and the epilogue applies the gate lane by lane, so the [T, 2 * inter]
 // intermediate never exists.
@@ -73,7 +73,16 @@ struct GemmParams {
     // The gated epilogue: g * sigmoid(slope * g) * (u + offset) with g = min(gate, limit), u = clamp(up, +-limit)
     // when limit > 0.  The defaults are SwiGLU.
     float act_slope = 1.0f, act_limit = 0.0f, act_offset = 0.0f;
+    int act_gelu = 0;  // 1: the gate is the tanh form of GELU, g * sigmoid(2 sqrt(2 / pi) (g + 0.044715 g^3))
 };
+
+// The gate of the fused gated unit: g * sigmoid(slope * g), or the tanh form of GELU, which is the same expression
+// with slope * g replaced by 2 sqrt(2 / pi) (g + 0.044715 g^3), since 0.5 (1 + tanh(y)) = sigmoid(2 y).  The result
+// is rounded to bfloat16, so the fast exponential and division (a few ulp of float32) cost no accuracy here.
+__device__ __forceinline__ float gate_activation(float g, float slope, int gelu) {
+    const float inside = gelu ? 1.5957691216057308f * g * fmaf(0.044715f * g, g, 1.0f) : slope * g;
+    return __fdividef(g, 1.0f + __expf(-inside));
+}
 
 template <int BLOCK_T, bool DUAL>
 __global__ void __launch_bounds__(GEMM_THREADS)
@@ -216,14 +225,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                         for (int c = 0; c < 16; ++c) {
                             const int t = t0 + c0 + c;
                             if (t < p.tokens) {
-                                // The result is rounded to bfloat16, so the fast exponential and
-                                // division (a few ulp of float32) cost no accuracy here.
                                 float g = gate[c], u = up[c];
                                 if (p.act_limit > 0.0f) {
                                     g = fminf(g, p.act_limit);
                                     u = fminf(fmaxf(u, -p.act_limit), p.act_limit);
                                 }
-                                const float activated = __fdividef(g, 1.0f + __expf(-p.act_slope * g));
+                                const float activated = gate_activation(g, p.act_slope, p.act_gelu);
                                 out[static_cast<size_t>(t) * p.outs + n] = __float2bfloat16_rn(activated * (u + p.act_offset));
                             }
                         }
@@ -416,7 +423,7 @@ gemm_tcgen05_stacked_swiglu_kernel(const __grid_constant__ CUtensorMap map_w, co
                         const int t = t0 + c0 + c;
                         if (t < p.tokens) {
                             const float g = gate[c] + (add ? other_half[(c0 + c) * BLOCK_N + quarter * 32 + lane] : 0.0f);
-                            const float activated = __fdividef(g, 1.0f + __expf(-g));
+                            const float activated = gate_activation(g, 1.0f, p.act_gelu);
                             out[static_cast<size_t>(t) * p.outs + n] = __float2bfloat16_rn(activated * exchange[(c0 + c) * STACK_ROWS + feature]);
                         }
                     }
@@ -581,7 +588,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid
 #pragma unroll
                         for (int c = 0; c < 16; ++c)
                             if (t0 + c0 + c < p.tokens) {
-                                const float activated = __fdividef(gate[c], 1.0f + __expf(-gate[c]));
+                                const float activated = gate_activation(gate[c], 1.0f, p.act_gelu);
                                 out[static_cast<size_t>(t0 + c0 + c) * p.outs + n] = __float2bfloat16_rn(activated * up[c]);
                             }
                     }
@@ -791,7 +798,7 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const 
 #pragma unroll
                         for (int c = 0; c < 16; ++c)
                             if (t0 + c0 + c < p.tokens) {
-                                const float activated = __fdividef(gate[c], 1.0f + __expf(-gate[c]));
+                                const float activated = gate_activation(gate[c], 1.0f, p.act_gelu);
                                 out[static_cast<size_t>(t0 + c0 + c) * p.outs + n] = __float2bfloat16_rn(activated * up[c]);
                             }
                     }
@@ -1009,24 +1016,26 @@ ME_EXPORT int me_gemm_tcgen05_persistent(const void* map_w, const void* map_x, f
 // act[t][n] (bfloat16) = silu(x . w[n]) * (x . w[dual_row_offset + n]) by persistent CTA pairs.
 // Weight and activation maps have boxes of 128 rows.
 ME_EXPORT int me_gemm_tcgen05_persistent_swiglu(const void* map_w, const void* map_x, void* act, int tokens, int outs,
-                                                int inner, int dual_row_offset, int group, cudaStream_t stream) {
+                                                int inner, int dual_row_offset, int group, int gelu, cudaStream_t stream) {
     if (tokens <= 0 || outs <= 0) return 0;
     alignas(64) CUtensorMap w, x;
     memcpy(&w, map_w, sizeof(w));
     memcpy(&x, map_x, sizeof(x));
     GemmParams p{act, tokens, outs, (inner + BLOCK_K - 1) / BLOCK_K, 0, dual_row_offset, 0, 0, 1, 0, 0, 0};
+    p.act_gelu = gelu;
     return launch_persistent<true>(w, x, p, group, stream);
 }
 
 // act[t][n] (bfloat16) = silu(x . w[n]) * (x . w[dual_row_offset + n]) for n < outs.
 ME_EXPORT int me_gemm_tcgen05_swiglu(const void* map_w, const void* map_x, void* act, int tokens, int outs, int inner,
-                                     int dual_row_offset, int block_t, cudaStream_t stream) {
+                                     int dual_row_offset, int block_t, int gelu, cudaStream_t stream) {
     if (tokens <= 0 || outs <= 0) return 0;
     alignas(64) CUtensorMap w, x;
     memcpy(&w, map_w, sizeof(w));
     memcpy(&x, map_x, sizeof(x));
     GemmParams p{act, tokens, outs, (inner + BLOCK_K - 1) / BLOCK_K, 0, dual_row_offset, 0, 0, 1};
     p.k_blocks_per_split = p.k_blocks;
+    p.act_gelu = gelu;
     if (block_t == 256) return launch<256, true>(w, x, p, 1, stream);  // both accumulators fill all 512 TMEM columns
     if (block_t == 128) return launch<128, true>(w, x, p, 1, stream);
     return ME_ERR_ARGUMENT;
@@ -1070,12 +1079,13 @@ static int launch_stacked_halves(const CUtensorMap& map_w, const CUtensorMap& ma
 // 32 or 64), the reduction in one CTA or (`halves` 2, block_t 16) in the two CTAs of a cluster.
 // The weight map has boxes of 64 rows.
 ME_EXPORT int me_gemm_tcgen05_stacked_swiglu(const void* map_w, const void* map_x, void* act, int tokens, int outs,
-                                             int inner, int dual_row_offset, int block_t, int halves, cudaStream_t stream) {
+                                             int inner, int dual_row_offset, int block_t, int halves, int gelu, cudaStream_t stream) {
     if (tokens <= 0 || outs <= 0) return 0;
     alignas(64) CUtensorMap w, x;
     memcpy(&w, map_w, sizeof(w));
     memcpy(&x, map_x, sizeof(x));
     GemmParams p{act, tokens, outs, (inner + BLOCK_K - 1) / BLOCK_K, 0, dual_row_offset, 0, 0, 1, 0};
+    p.act_gelu = gelu;
     if (halves == 2) return block_t == 16 ? launch_stacked_halves<16>(w, x, p, stream) : ME_ERR_ARGUMENT;
     if (halves != 1) return ME_ERR_ARGUMENT;
     switch (block_t) {

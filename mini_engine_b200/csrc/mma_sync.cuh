@@ -1,0 +1,43 @@
+// Warp-level tensor-core pieces shared by the mma.sync attention kernels: asynchronous 16-byte copies into
+// shared memory, the bank-conflict-free placement of 16-byte chunks, ldmatrix and the bfloat16 m16n8k16 product.
+#pragma once
+
+#include "common.cuh"
+
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+// 16-byte chunks of a row are permuted by the row's low bits so that the eight rows an
+// ldmatrix reads fall into different banks.
+template <int D>
+__device__ __forceinline__ int swizzled(int row, int chunk) {
+    return row * (D / 8) + (chunk ^ (row & 7));
+}
+
+__device__ __forceinline__ void cp_async_16(void* dst, const void* src, bool valid) {
+    const int bytes = valid ? 16 : 0;  // 0: the destination is filled with zeros
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_addr(dst)), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_addr(p)));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_addr(p)));
+}
+__device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// The same placement for rows whose width is known at run time (`chunks` 16-byte chunks a row, a multiple of 8).
+__device__ __forceinline__ int swizzled_at(int row, int chunk, int chunks) { return row * chunks + (chunk ^ (row & 7)); }

@@ -14,6 +14,7 @@ from typing import Any
 
 import torch
 
+from mini_engine_b200.csrc import build
 from mini_engine_b200.csrc.build import load_library
 
 F32, BF16 = 0, 1
@@ -104,7 +105,15 @@ def raise_on_device_error() -> None:
     """Ask the tensor-core and attention libraries that are loaded whether a kernel gave up a
     bounded wait since the last call, and raise if one did: what such a kernel wrote is invalid.
     Reads a flag from the device, so it waits for the work in flight."""
-    for what, code in (("tensor-core product", tensor_core.take_error()), ("attention", attention_bf16.take_error())):
+    latent = 0
+    if "latent_attention_bf16" in build._loaded:
+        held = c_int(0)
+        status = _fn("latent_attention_bf16", "me_latent_attention_bf16_take_error", [ctypes.POINTER(c_int)])(ctypes.byref(held))
+        if status != 0:
+            raise KernelError(f"could not read the latent attention kernel's error flag (CUDA error {status})")
+        latent = held.value
+    for what, code in (("tensor-core product", tensor_core.take_error()), ("attention", attention_bf16.take_error()),
+                       ("latent attention", latent)):  # fmt: skip
         if code:
             raise KernelError(
                 f"a {what} kernel ran into the limit of a wait (code {code}): the results since the last check are invalid"
@@ -438,8 +447,8 @@ def gemm_tensor_core(plan, x: torch.Tensor, out: torch.Tensor, splits: int) -> N
     tensor_core.gemm(plan, x, out, splits)
 
 
-def gemm_tensor_core_swiglu(plan, x: torch.Tensor, act: torch.Tensor) -> None:
-    tensor_core.gemm_swiglu(plan, x, act)
+def gemm_tensor_core_swiglu(plan, x: torch.Tensor, act: torch.Tensor, activation: str = "silu") -> None:
+    tensor_core.gemm_swiglu(plan, x, act, activation=activation)
 
 
 # -------------------------------------------------------------------------------- attention
@@ -504,6 +513,11 @@ def paged_attention(
     tokens' own keys are already in the cache).  Chooses the kernel by dtype and sizes.  ``value_dim``,
     ``sink``, ``gate``, ``slopes`` and ``sink_values`` as in :func:`paged_attention_generic`; value heads of another
     width than the key heads and values inside the key rows (``v_pages=None``) take that kernel."""
+    if v_pages is None and q.dtype == torch.bfloat16 and latent_attention_supports(head_dim, value_dim, kv_heads):
+        if sink or slopes is not None or sink_values is not None:
+            raise KernelError("attention over latent rows takes a window and a gate per head, no sink and no distance bias")
+        latent_attention_bf16(q, k_pages, block_table, ctx, out, heads, head_dim, value_dim, scale, window, gate)
+        return
     if v_pages is not None and q.dtype == torch.bfloat16 and value_dim in (None, head_dim):
         if attention_bf16.supports(head_dim, heads, kv_heads):
             attention_bf16.paged_attention(
@@ -515,6 +529,58 @@ def paged_attention(
         q, k_pages, v_pages, block_table, ctx.entry_of_token, ctx.positions, out, heads, kv_heads, head_dim,
         scale, window, value_dim=value_dim, sink=sink, gate=gate, slopes=slopes, sink_values=sink_values,
     )  # fmt: skip
+
+
+LATENT_ROWS, LATENT_SPAN = 32, 256  # (token, head) pairs of a CTA of the kernel below; keys of a CTA of a split request
+
+
+def latent_attention_supports(width: int, rank: int | None, kv_heads: int = 1) -> bool:
+    """Whether the tensor-core kernel takes rows of ``width`` elements whose first ``rank`` are the values."""
+    return kv_heads == 1 and rank in (128, 256, 384, 512) and width % 64 == 0 and rank <= width and (160 * width + 2048) * 2 + 1024 <= 226 * 1024
+
+
+def latent_attention_bf16(q, pages, block_table, ctx, out, heads: int, width: int, rank: int, scale: float, window: int,
+                          gate: torch.Tensor | None = None) -> None:  # fmt: skip
+    """Attention of the batch's new tokens over a cache of one latent row per token (``pages [pages, 1, page_size,
+    width]``) that is key and, in its first ``rank`` elements, value for every head; ``q [T, heads * width]``, ``out [T,
+    heads * rank]``, ``gate`` float32 ``[T, heads]``.  Entries that bring one token split their keys over several CTAs
+    (spans of ``LATENT_SPAN`` keys by absolute position), the others take one CTA per 32 (token, head) pairs; a step
+    that holds both kinds is two launches, each over its own list of entries."""
+    for name, t in (("q", q), ("out", out), ("pages", pages)):
+        if t.dtype != torch.bfloat16 or not t.is_contiguous():
+            raise KernelError(f"{name} must be contiguous bfloat16")
+    if pages.dim() != 4 or pages.shape[1] != 1 or pages.shape[3] != width:
+        raise KernelError(f"latent pages {tuple(pages.shape)} are not [pages, 1, page_size, {width}]")
+    if q.shape != (out.shape[0], heads * width) or out.shape[1] != heads * rank:
+        raise KernelError("q must be [tokens, heads * width] and out [tokens, heads * rank]")
+    if gate is not None:
+        _need(gate, torch.float32, "gate")
+        if gate.shape != (q.shape[0], heads):
+            raise KernelError("gate must be [tokens, heads]")
+    _need(block_table, torch.int32, "block_table")
+    fn = _fn("latent_attention_bf16", "me_latent_attention_bf16",
+             [c_void_p] * 10 + [c_float] + [c_int] * 10 + [c_void_p])  # fmt: skip
+    decodes = ctx.num_entries if ctx.all_decode else getattr(ctx, "num_decode_entries", 0)
+    if decodes == ctx.num_entries:
+        launches = [(True, decodes, None, 1)]
+    elif decodes:
+        launches = [(True, decodes, ctx.decode_entries, 1), (False, ctx.num_entries - decodes, ctx.portion_entries, ctx.max_query_len)]
+    else:
+        launches = [(False, ctx.num_entries, None, ctx.max_query_len)]
+    for split, entries, ids, longest in launches:
+        partials = counters = None
+        max_splits = 1
+        if split:
+            keys = min(window, ctx.max_context_len) if window > 0 else ctx.max_context_len
+            max_splits = (keys - 1) // LATENT_SPAN + 2 if window > 0 else -(-keys // LATENT_SPAN)
+            partials = ctx.workspace.growing("latent.partials", (ctx.num_entries, heads, max_splits, rank + 2), torch.float32)
+            counters = ctx.workspace.zeroed("latent.counters", ctx.num_entries * (-(-heads // LATENT_ROWS)))
+        code = fn(
+            _ptr(q), _ptr(pages), _ptr(block_table), _ptr(ctx.cu_tokens), _ptr(ctx.context_lens), _ptr(out), _ptr(gate),
+            _ptr(partials), _ptr(counters), _ptr(ids), scale, entries, longest, heads, width, rank, pages.shape[2],
+            block_table.shape[1], window, 1 if split else 0, max_splits, _stream(),
+        )  # fmt: skip
+        _check(code, "latent_attention_bf16")
 
 
 def latent_down_finish(
@@ -556,6 +622,9 @@ def latent_down_finish(
     _check(code, "latent_down_finish")
 
 
+HEAD_PRODUCT_TENSOR = True  # tests set it to False to run the plain kernel where the tensor-core one would be taken
+
+
 def head_product(
     x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, *, tail: int = 0, cos_sin: torch.Tensor | None = None,
 ) -> None:  # fmt: skip
@@ -580,6 +649,15 @@ def head_product(
         rotary_dim = 2 * cos_sin.shape[1] if cos_sin.dim() == 3 else -1
         if cos_sin.dim() != 3 or cos_sin.shape[0] != tokens or cos_sin.shape[2] != 2 or not 2 <= rotary_dim <= tail:
             raise KernelError(f"cos_sin {tuple(cos_sin.shape)} is not [tokens, rotary_dim / 2, 2] with rotary_dim <= tail")
+    if HEAD_PRODUCT_TENSOR and weight.dtype == torch.bfloat16 and inner % 64 == 0 and outs % 8 == 0 and tail % 8 == 0 and 64 * inner * 2 + 32768 <= 200 * 1024:
+        fn = _fn("latent_attention_bf16", "me_head_product_bf16",
+                 [c_void_p, c_int, c_int, c_longlong, c_void_p, c_void_p, c_void_p] + [c_int] * 6 + [c_void_p])  # fmt: skip
+        code = fn(
+            _ptr(x), _type_code(x.dtype), splits, stride, _ptr(weight), _ptr(cos_sin), _ptr(out), tokens, heads, inner,
+            outs, tail, rotary_dim, _stream(),
+        )  # fmt: skip
+        _check(code, "head_product_bf16")
+        return
     fn = _fn("latent_attention", "me_head_product",
              [c_void_p, c_int, c_int, c_longlong, c_void_p, c_void_p, c_void_p] + [c_int] * 7 + [c_void_p])  # fmt: skip
     code = fn(

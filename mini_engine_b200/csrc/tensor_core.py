@@ -58,15 +58,15 @@ def _library():
         lib.me_make_tensor_map.restype = c_int
         lib.me_gemm_tcgen05.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]
         lib.me_gemm_tcgen05.restype = c_int
-        lib.me_gemm_tcgen05_swiglu.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]
+        lib.me_gemm_tcgen05_swiglu.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]
         lib.me_gemm_tcgen05_swiglu.restype = c_int
         lib.me_gemm_tcgen05_pair_split.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]
         lib.me_gemm_tcgen05_pair_split.restype = c_int
         lib.me_gemm_tcgen05_persistent.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]
         lib.me_gemm_tcgen05_persistent.restype = c_int
-        lib.me_gemm_tcgen05_persistent_swiglu.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]
+        lib.me_gemm_tcgen05_persistent_swiglu.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]
         lib.me_gemm_tcgen05_persistent_swiglu.restype = c_int
-        lib.me_gemm_tcgen05_stacked_swiglu.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]
+        lib.me_gemm_tcgen05_stacked_swiglu.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]
         lib.me_gemm_tcgen05_stacked_swiglu.restype = c_int
         lib.me_gemm_tcgen05_grouped.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_int, c_int,
                                                 ctypes.c_float, ctypes.c_float, ctypes.c_float, c_void_p]
@@ -178,9 +178,11 @@ def gemm(plan: GemmPlan, x: torch.Tensor, out: torch.Tensor, splits: int, group:
         raise RuntimeError(f"tensor-core product failed to launch (code {code})")
 
 
-def gemm_swiglu(plan: GemmPlan, x: torch.Tensor, act: torch.Tensor, halves: int | None = None, group: int | None = None) -> None:
+def gemm_swiglu(
+    plan: GemmPlan, x: torch.Tensor, act: torch.Tensor, halves: int | None = None, group: int | None = None, activation: str = "silu"
+) -> None:
     """``act = silu(x @ gate^T) * (x @ up^T)`` in bfloat16, gate/up being the halves of the
-    plan's weight.  ``halves`` (1 or 2) pins how many CTAs share a reduction of the few-token kernel
+    plan's weight; ``activation="gelu_tanh"`` gates with the tanh form of GELU instead.  ``halves`` (1 or 2) pins how many CTAs share a reduction of the few-token kernel
     instead of the rule's choice: the kernel tests run both forms, the kernel bench times them."""
     _check_x(plan, x)
     tokens = x.shape[0]
@@ -188,6 +190,9 @@ def gemm_swiglu(plan: GemmPlan, x: torch.Tensor, act: torch.Tensor, halves: int 
         raise RuntimeError("this plan was not made for a gated product")
     if act.dtype != torch.bfloat16 or tuple(act.shape) != (tokens, plan.dual_rows) or not act.is_contiguous():
         raise RuntimeError(f"activation output {tuple(act.shape)} does not fit [{tokens}, {plan.dual_rows}] bfloat16")
+    if activation not in ("silu", "gelu_tanh"):
+        raise RuntimeError(f"the gated product's epilogue knows 'silu' and 'gelu_tanh', got {activation!r}")
+    gelu = 1 if activation == "gelu_tanh" else 0
     stream = _ops_stream()
     if tokens <= STACKED_MAX_TOKENS:
         tile = token_tile(tokens)
@@ -195,18 +200,18 @@ def gemm_swiglu(plan: GemmPlan, x: torch.Tensor, act: torch.Tensor, halves: int 
             halves = 2 if tokens <= STACKED_HALVES_MAX_TOKENS and plan.inner >= 2 * BLOCK_K else 1
         code = _library().me_gemm_tcgen05_stacked_swiglu(
             plan.map_half, _activation_map(x, tile), act.data_ptr(), tokens, plan.dual_rows, plan.inner, plan.dual_rows,
-            tile, halves, stream,
+            tile, halves, gelu, stream,
         )  # fmt: skip
     elif tokens > PAIR_MIN_TOKENS:
         code = _library().me_gemm_tcgen05_persistent_swiglu(
             plan.map, _activation_map(x, 128), act.data_ptr(), tokens, plan.dual_rows, plan.inner, plan.dual_rows,
-            PAIR_GROUP_TOKEN_TILES_GATED if group is None else group, stream,
+            PAIR_GROUP_TOKEN_TILES_GATED if group is None else group, gelu, stream,
         )  # fmt: skip
     else:
         tile = 128  # 65 to 128 tokens: lone CTAs with gate and up sums side by side in tensor memory
         code = _library().me_gemm_tcgen05_swiglu(
             plan.map, _activation_map(x, tile), act.data_ptr(), tokens, plan.dual_rows, plan.inner, plan.dual_rows,
-            tile, stream,
+            tile, gelu, stream,
         )
     _count_launch()
     if code != 0:

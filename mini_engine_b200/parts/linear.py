@@ -77,13 +77,15 @@ class GatedLinear:
     """``silu(x Wg^T) * (x Wu^T)`` from the row-concatenated weight ``[2 * inter, in]``; with a
     ``slope``, a ``limit`` or an ``offset`` the gated unit of :func:`ops.swiglu` with those constants
     (as a kernel of its own behind the product: the fused epilogue is SwiGLU proper).  ``activation``
-    ``"gelu_tanh"`` gates with the tanh form of GELU instead of ``g * sigmoid(slope * g)``."""
+    ``"gelu_tanh"`` gates with the tanh form of GELU instead of ``g * sigmoid(slope * g)``; the fused epilogue
+    knows it too."""
 
     def __init__(
         self, gate_up: torch.Tensor, slope: float = 1.0, limit: float | None = None, offset: float = 0.0, activation: str = "silu"
     ):
         self.slope, self.limit, self.offset, self.activation = slope, limit, offset, activation
-        self.plain = slope == 1.0 and limit is None and offset == 0.0 and activation == "silu"
+        # the fused epilogue knows SwiGLU proper and the tanh-GELU gate
+        self.plain = slope == 1.0 and limit is None and offset == 0.0 and activation in ("silu", "gelu_tanh")
         self.weight = gate_up
         self.inter = gate_up.shape[0] // 2
         self.in_features = gate_up.shape[1]
@@ -99,7 +101,7 @@ class GatedLinear:
         act = ctx.buffer(name + ".act", (tokens, self.inter), x.dtype)
         fused = tokens >= GATED_FUSED_MIN_TOKENS and (tokens > DECODE_TOKENS or self.inter >= GATED_STACKED_MIN_FEATURES)
         if self.tensor_core and fused and self.plain:
-            ops.gemm_tensor_core_swiglu(self.plan, x, act)
+            ops.gemm_tensor_core_swiglu(self.plan, x, act, self.activation)
             return act
         both = self.linear.forward(x, ctx, name + ".gate_up")
         ops.swiglu(both, act, self.slope, self.limit, self.offset, activation=self.activation)

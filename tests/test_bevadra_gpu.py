@@ -536,6 +536,133 @@ def test_tensor_core_attention_with_bias_sinks_and_element_gates(head_dim, heads
     assert error < 2e-2, f"relative error {error:.3g}"
 
 
+@pytest.mark.parametrize("rank,rot", [(128, 64), (256, 64), (512, 64), (384, 0)])
+@pytest.mark.parametrize("heads,page", [(5, 4), (16, 16), (40, 16)])
+@pytest.mark.parametrize("news", [[1, 1, 1, 1], [90, 5, 130, 2], [1, 40, 1, 7]])
+@pytest.mark.parametrize("window", [0, 70, 300])
+def test_tensor_core_attention_over_latent_rows(rank, rot, heads, page, news, window):
+    """The bfloat16 kernel whose score rows are (token, head) pairs over one cached row per token that is key and,
+    in its first elements, value: prompt portions, requests of one token whose keys are split over several CTAs (the
+    longest context spans three of them), and both in one step, with a gate per head, over shuffled pages whose free
+    places hold large numbers, against float64.  One key of every request stands out for the first head."""
+    from test_kernels_gpu import fake_context
+
+    from mini_engine_b200.csrc import ops
+
+    width = rank + rot
+    g = torch.Generator().manual_seed(rank + heads + page + len(news) + window + news[1])
+    lengths = [700, 90, 130, 300]
+    total_pages = sum(-(-n // page) for n in lengths) + 3
+    order = torch.randperm(total_pages, generator=g).tolist()
+    pages = torch.full((total_pages, 1, page, width), 1e4).to(torch.bfloat16)
+    table = torch.full((len(lengths), max(-(-n // page) for n in lengths) + 1), -1, dtype=torch.int32)
+    q_rows, want_rows, gate_rows, entry_of, positions = [], [], [], [], []
+    for b, (n, new) in enumerate(zip(lengths, news)):
+        q = (0.5 * torch.randn(n, heads, width, generator=g)).to(torch.bfloat16)
+        k = torch.randn(n, 1, width, generator=g).to(torch.bfloat16)
+        far = max(n - (window or n) + 1, 0) + 2  # a key near the far end of what the last queries see
+        k[far, 0] = (k[far, 0].float() + 0.3 * q[n - 1, 0].float()).to(torch.bfloat16)
+        gate = torch.rand(n, heads, generator=g)
+        for i in range(-(-n // page)):
+            table[b, i] = order.pop()
+        for p in range(n):
+            pages[table[b, p // page], 0, p % page] = k[p, 0]
+        want = plain_biased_attention(q.double(), k.double(), k[:, :, :rank].double(), width**-0.5, window or None, gate=gate)
+        q_rows.append(q[n - new :]), want_rows.append(want[n - new :]), gate_rows.append(gate[n - new :])
+        entry_of += [b] * new
+        positions += list(range(n - new, n))
+    data = dict(new_counts=news, lengths=lengths, entry_of=torch.tensor(entry_of, dtype=torch.int32).cuda(),
+                positions=torch.tensor(positions, dtype=torch.int32).cuda())  # fmt: skip
+    q_all = torch.cat(q_rows).reshape(-1, heads * width).contiguous().cuda()
+    want = torch.cat(want_rows).reshape(-1, heads * rank).float()
+    out = torch.full((q_all.shape[0], heads * rank), float("nan"), dtype=torch.bfloat16, device="cuda")
+    assert ops.latent_attention_supports(width, rank)
+    for _ in range(2):  # the second run finds the arrival counters as the first left them
+        out.fill_(float("nan"))
+        ops.paged_attention(
+            q=q_all, k_pages=pages.cuda(), v_pages=None, block_table=table.cuda(), ctx=fake_context(data), out=out, heads=heads,
+            kv_heads=1, head_dim=width, scale=width**-0.5, window=window, value_dim=rank, gate=torch.cat(gate_rows).contiguous().cuda(),
+        )  # fmt: skip
+        torch.cuda.synchronize()
+        ops.raise_on_device_error()
+        error = float((out.float().cpu() - want).abs().max()) / float(want.abs().max())
+        assert error < 2e-2, f"relative error {error:.3g}"
+
+
+@pytest.mark.parametrize("window", [5, 64, 65, 200, 257])
+@pytest.mark.parametrize("offset", ["just_inside", "just_outside", "far", "itself"])
+def test_a_key_that_stands_out_at_the_windows_edge_on_tensor_cores(window, offset):
+    """As above for the tensor-core kernel over latent rows: the marked value is in the output exactly when its key
+    is inside the window, for a query inside a portion and for one that comes alone (split over spans of keys)."""
+    from test_kernels_gpu import fake_context
+
+    from mini_engine_b200.csrc import ops
+
+    torch.manual_seed(window)
+    T, H, W, R, page = 600, 6, 192, 128, 16
+    query = 590
+    target = {"just_inside": query - window + 1, "just_outside": query - window, "far": 3, "itself": query}[offset]
+    q, k = 0.1 * torch.randn(T, H, W), 0.1 * torch.randn(T, 1, W)
+    k[:, :, 0] = 0.0
+    q[:, :, 0] = 0.0
+    k[target] += 4.0 * q[query, 0] / q[query, 0].norm()
+    q[query] = 6.0 * q[query] / q[query].norm(dim=-1, keepdim=True)
+    k[target, :, 0] = 100.0
+    q, k = q.to(torch.bfloat16), k.to(torch.bfloat16)
+    visible = 0 <= query - target < window
+    want = plain_biased_attention(q.double(), k.double(), k[:, :, :R].double(), 1.0, window).float()
+    generator = torch.Generator().manual_seed(T)
+    pages, table = paged(k.float(), page, 3 * (-(-T // page)), generator)
+    for new, length in ((1, query + 1), (25, query + 5)):
+        rows = list(range(length - new, length))
+        data = dict(new_counts=[new], lengths=[length], entry_of=torch.zeros(new, dtype=torch.int32).cuda(),
+                    positions=torch.tensor(rows, dtype=torch.int32).cuda())  # fmt: skip
+        out = torch.full((new, H * R), float("nan"), dtype=torch.bfloat16, device="cuda")
+        ops.paged_attention(
+            q=q[rows].reshape(new, H * W).contiguous().cuda(), k_pages=pages.to(torch.bfloat16).cuda(), v_pages=None,
+            block_table=table.view(1, -1).cuda(), ctx=fake_context(data), out=out, heads=H, kv_heads=1, head_dim=W, scale=1.0,
+            window=window, value_dim=R,
+        )  # fmt: skip
+        torch.cuda.synchronize()
+        got = out.float().cpu().view(new, H, R)
+        assert (got[rows.index(query), 0, 0] > 50.0) == visible, f"the marked value is {'missing' if visible else 'seen'}"
+        assert torch.allclose(got, want[rows], atol=2.0, rtol=2e-2)
+
+
+@pytest.mark.parametrize("heads,inner,outs,tail,dims", [(3, 128, 200, 16, 8), (2, 512, 128, 0, 0), (5, 64, 520, 64, 64), (1, 192, 8, 8, 0)])
+@pytest.mark.parametrize("tokens", [1, 70, 130])
+def test_products_per_head_on_tensor_cores(heads, inner, outs, tail, dims, tokens):
+    """The bfloat16 products per head whose inner size is a multiple of 64 run on tensor cores: from partial sums and
+    from rounded rows, with a rotated tail, at token counts around the tile of 64."""
+    from mini_engine_b200.csrc import ops
+
+    torch.manual_seed(heads + inner + tokens)
+    x = torch.randn(2, tokens, heads * (inner + tail))
+    weight = torch.randn(heads, inner, outs).to(torch.bfloat16)
+    positions = torch.arange(30, 30 + tokens)
+    table = None
+    if dims:
+        freq = torch.tensor([700.0 ** (-2.0 * i / dims) for i in range(dims // 2)], dtype=torch.float64)
+        angle = positions.double().view(-1, 1) * freq
+        table = torch.stack((torch.cos(angle), torch.sin(angle)), dim=-1).float()
+    rows = x.double().sum(0).view(tokens, heads, inner + tail)
+    rounded = rows[..., :inner].to(torch.bfloat16).double()
+    want = torch.einsum("thk,hkn->thn", rounded, weight.double())
+    if tail:
+        rotated = plain.rotate_half(rows[..., inner:], positions, 700.0, dims) if dims else rows[..., inner:]
+        want = torch.cat((want, rotated), dim=-1)
+    out = torch.full((tokens, heads * (outs + tail)), float("nan"), dtype=torch.bfloat16, device="cuda")
+    ops.head_product(cuda(x), weight.cuda(), out, tail=tail, cos_sin=cuda(table))
+    limit = 1e-2 * float(want.abs().max())
+    assert torch.allclose(out.float().cpu().double().view(tokens, heads, -1), want, atol=limit)
+    if not tail:
+        single = x.sum(0).to(torch.bfloat16)
+        out.fill_(float("nan"))
+        ops.head_product(single.cuda(), weight.cuda(), out)
+        want = torch.einsum("thk,hkn->thn", single.double().view(tokens, heads, inner), weight.double())
+        assert torch.allclose(out.float().cpu().double().view(tokens, heads, -1), want, atol=limit)
+
+
 # ---------------------------------------------------------------------- mechanisms alone: the latent layer
 
 

@@ -144,18 +144,22 @@ def test_gemm_tensor_core_finds_one_large_product():
         (65, 160, 96), (128, 128, 64), (300, 300, 264), (2048, 2600, 136),
     ],
 )  # fmt: skip
-def test_gemm_tensor_core_swiglu(tokens, inter, inner):
+@pytest.mark.parametrize("activation", ["silu", "gelu_tanh"])
+def test_gemm_tensor_core_swiglu(tokens, inter, inner, activation):
     from mini_engine_b200.csrc import tensor_core
 
     torch.manual_seed(3)
     x = torch.randn(tokens, inner, device="cuda").to(torch.bfloat16)
     w = (torch.randn(2 * inter, inner, device="cuda") * 0.2).to(torch.bfloat16)
     act = torch.empty(tokens, inter, device="cuda", dtype=torch.bfloat16)
-    tensor_core.gemm_swiglu(tensor_core.GemmPlan(w, dual_rows=inter), x, act)
+    tensor_core.gemm_swiglu(tensor_core.GemmPlan(w, dual_rows=inter), x, act, activation=activation)
     assert tensor_core.take_error() == 0
     both = x.double() @ w.double().T
     gate, up = both[:, :inter], both[:, inter:]
-    want = gate * torch.sigmoid(gate) * up
+    if activation == "silu":
+        want = gate * torch.sigmoid(gate) * up
+    else:  # every fused epilogue (few tokens stacked, lone CTAs, persistent pairs) with the tanh form of GELU as the gate
+        want = 0.5 * gate * (1.0 + torch.tanh((2.0 / torch.pi) ** 0.5 * (gate + 0.044715 * gate**3))) * up
     assert rel_error(act, want) < 6e-3  # one rounding to bfloat16
 
 
