@@ -365,6 +365,123 @@ __global__ void __launch_bounds__(256) add_layernorm_kernel(LayerNormArgs a) {
         out_ptr[i] = from_float<OutT>(fmaf((row_cache[i] - mean) * inv, a.weight[i], a.bias[i]));
 }
 
+// The same over LANES "lanes" of four consecutive columns each, as in add_rmsnorm_kernel: lane v holds columns
+// 4v..4v+3 (+ 4 LANES j) and one partial sum; a warp's 32 lanes are added by a butterfly and the warps in ascending
+// order.  LANES follows from the width alone, THREADS from the number of rows (one lane per thread for few rows,
+// so that every load of a row is in flight at once; 256 threads that play LANES / 256 lanes each for many rows),
+// and both give the same bits.  Every pointer is 16-byte aligned, the width a multiple of 4, at most
+// MAX_UNROLLED_SPLITS partial sums per sublayer.
+template <int LANES, int THREADS>
+__device__ __forceinline__ float lanes_total(const float (&mine)[LANES / THREADS], float* warp_partial) {
+    constexpr int PLAYED = LANES / THREADS;
+#pragma unroll
+    for (int k = 0; k < PLAYED; ++k) {
+        const float warp_total = warp_sum(mine[k]);
+        if ((threadIdx.x & 31) == 0) warp_partial[k * (THREADS / 32) + (threadIdx.x >> 5)] = warp_total;
+    }
+    __syncthreads();
+    float total = 0.0f;
+#pragma unroll
+    for (int w = 0; w < LANES / 32; ++w) total += warp_partial[w];
+    __syncthreads();
+    return total;
+}
+
+__device__ __forceinline__ void add4(float4& a, const float4& b) { a.x += b.x, a.y += b.y, a.z += b.z, a.w += b.w; }
+
+template <typename OutT, int LANES, int THREADS>
+__global__ void __launch_bounds__(THREADS) add_layernorm_vec_kernel(LayerNormArgs a) {
+    constexpr int PLAYED = LANES / THREADS;
+    extern __shared__ float row_cache[];  // [hidden]
+    __shared__ float warp_partial[LANES / 32];
+    const int out_row = blockIdx.x;
+    pdl_trigger();
+    const int src = a.rows ? a.rows[out_row] : out_row;
+    pdl_wait();
+    const size_t offset = static_cast<size_t>(src) * a.hidden;
+    float* x_row = a.x + offset;
+    const bool write_back = !a.rows && (a.first_splits > 0 || a.second_splits > 0 || a.add_bias != nullptr);
+    float sums[PLAYED];
+#pragma unroll
+    for (int k = 0; k < PLAYED; ++k) sums[k] = 0.0f;
+    for (int base = 0; base < a.hidden; base += LANES * 4) {
+#pragma unroll
+        for (int k = 0; k < PLAYED; ++k) {
+            const int i = base + (k * THREADS + threadIdx.x) * 4;
+            if (i >= a.hidden) continue;
+            float4 v = *reinterpret_cast<const float4*>(x_row + i);
+            float4 one[MAX_UNROLLED_SPLITS], two[MAX_UNROLLED_SPLITS];
+#pragma unroll
+            for (int s = 0; s < MAX_UNROLLED_SPLITS; ++s) {
+                if (s < a.first_splits) one[s] = *reinterpret_cast<const float4*>(a.first + s * a.first_stride + offset + i);
+                if (s < a.second_splits) two[s] = *reinterpret_cast<const float4*>(a.second + s * a.second_stride + offset + i);
+            }
+            float4 bias = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            if (a.add_bias) bias = *reinterpret_cast<const float4*>(a.add_bias + i);
+            if (a.first_splits > 0) {
+                float4 part = one[0];
+#pragma unroll
+                for (int s = 1; s < MAX_UNROLLED_SPLITS; ++s)
+                    if (s < a.first_splits) add4(part, one[s]);
+                if (a.add_bias) add4(part, bias);
+                add4(v, part);
+            } else if (a.add_bias) {
+                add4(v, bias);
+            }
+            if (a.second_splits > 0) {
+                float4 part = two[0];
+#pragma unroll
+                for (int s = 1; s < MAX_UNROLLED_SPLITS; ++s)
+                    if (s < a.second_splits) add4(part, two[s]);
+                add4(v, part);
+            }
+            *reinterpret_cast<float4*>(row_cache + i) = v;
+            if (write_back) *reinterpret_cast<float4*>(x_row + i) = v;
+            sums[k] += (v.x + v.y) + (v.z + v.w);
+        }
+    }
+    const float mean = lanes_total<LANES, THREADS>(sums, warp_partial) / static_cast<float>(a.hidden);
+#pragma unroll
+    for (int k = 0; k < PLAYED; ++k) sums[k] = 0.0f;
+    for (int base = 0; base < a.hidden; base += LANES * 4) {
+#pragma unroll
+        for (int k = 0; k < PLAYED; ++k) {
+            const int i = base + (k * THREADS + threadIdx.x) * 4;
+            if (i >= a.hidden) continue;
+            const float4 v = *reinterpret_cast<const float4*>(row_cache + i);
+            const float dx = v.x - mean, dy = v.y - mean, dz = v.z - mean, dw = v.w - mean;
+            sums[k] = fmaf(dx, dx, sums[k]), sums[k] = fmaf(dy, dy, sums[k]);
+            sums[k] = fmaf(dz, dz, sums[k]), sums[k] = fmaf(dw, dw, sums[k]);
+        }
+    }
+    const float inv = rsqrtf(lanes_total<LANES, THREADS>(sums, warp_partial) / static_cast<float>(a.hidden) + a.eps);
+    OutT* out_ptr = static_cast<OutT*>(a.out) + static_cast<size_t>(out_row) * a.hidden;
+    for (int i = threadIdx.x * 4; i < a.hidden; i += THREADS * 4) {
+        const float4 v = *reinterpret_cast<const float4*>(row_cache + i);
+        const float4 w = *reinterpret_cast<const float4*>(a.weight + i), b = *reinterpret_cast<const float4*>(a.bias + i);
+        store4(out_ptr + i, make_float4(fmaf((v.x - mean) * inv, w.x, b.x), fmaf((v.y - mean) * inv, w.y, b.y),
+                                        fmaf((v.z - mean) * inv, w.z, b.z), fmaf((v.w - mean) * inv, w.w, b.w)));
+    }
+}
+
+template <typename OutT, int LANES, int THREADS>
+static int launch_add_layernorm_vec(const LayerNormArgs& a, int count, cudaStream_t stream) {
+    const size_t smem = static_cast<size_t>(a.hidden) * sizeof(float);
+    auto kernel = add_layernorm_vec_kernel<OutT, LANES, THREADS>;
+    if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    return launch_kernel(kernel, count, THREADS, smem, stream, a);
+}
+
+template <typename OutT>
+static int launch_add_layernorm_lanes(const LayerNormArgs& a, int count, cudaStream_t stream) {
+    const bool many = count >= NORM_MANY_ROWS;
+    if (a.hidden > 2048)
+        return many ? launch_add_layernorm_vec<OutT, 1024, 256>(a, count, stream) : launch_add_layernorm_vec<OutT, 1024, 1024>(a, count, stream);
+    if (a.hidden > 1024)
+        return many ? launch_add_layernorm_vec<OutT, 512, 256>(a, count, stream) : launch_add_layernorm_vec<OutT, 512, 512>(a, count, stream);
+    return launch_add_layernorm_vec<OutT, 256, 256>(a, count, stream);
+}
+
 ME_EXPORT int me_add_layernorm(float* x, const float* first, int first_splits, long long first_stride,
                                const float* second, int second_splits, long long second_stride, const float* add_bias,
                                const float* weight, const float* bias, float eps, void* out, int out_type,
@@ -375,6 +492,15 @@ ME_EXPORT int me_add_layernorm(float* x, const float* first, int first_splits, l
     if ((first_splits > 0 && first == nullptr) || (second_splits > 0 && second == nullptr)) return ME_ERR_ARGUMENT;
     LayerNormArgs a{x, first, first_splits, (size_t)first_stride, second, second_splits, (size_t)second_stride,
                     add_bias, weight, bias, eps, out, rows, hidden};
+    // Which kernel runs depends on the width, on the alignment of the engine's persistent buffers and on whether
+    // the products were split more than eight ways, never on the rows of the step.
+    const bool vec = hidden % 4 == 0 && aligned16(x) && aligned16(weight) && aligned16(bias) && aligned16(out) &&
+                     aligned16(add_bias) && first_splits <= MAX_UNROLLED_SPLITS && second_splits <= MAX_UNROLLED_SPLITS &&
+                     (first_splits == 0 || (aligned16(first) && first_stride % 4 == 0)) &&
+                     (second_splits == 0 || (aligned16(second) && second_stride % 4 == 0));
+    if (vec)
+        return out_type == ME_BF16 ? launch_add_layernorm_lanes<__nv_bfloat16>(a, count, stream)
+                                   : launch_add_layernorm_lanes<float>(a, count, stream);
     if (out_type == ME_BF16) {
         auto kernel = add_layernorm_kernel<__nv_bfloat16>;
         if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -1021,6 +1147,53 @@ __global__ void __launch_bounds__(256) qk_wide_norm_rope_store_kernel(WideQkvArg
     }
 }
 
+// The same row without a norm and without a rotation: every column stands alone, so a thread takes four consecutive
+// columns of one token (grid: runs of 1,024 columns x tokens), adds their partial sums in ascending order and the
+// bias, and stores them where the kernel above would (the same bits).  Every segment of the row starts and ends at a
+// multiple of four columns, as does every head; all pointers are 16-byte aligned; at most MAX_UNROLLED_SPLITS sums.
+template <typename OutT>
+__global__ void __launch_bounds__(256) qkv_bias_store_kernel(WideQkvArgs a) {
+    const int token = blockIdx.y;
+    const int i = (blockIdx.x * 256 + threadIdx.x) * 4;
+    pdl_trigger();
+    pdl_wait();
+    if (i >= a.row_width) return;
+    const float* src = a.qkv + static_cast<size_t>(token) * a.row_width + i;
+    float4 part[MAX_UNROLLED_SPLITS];
+#pragma unroll
+    for (int s = 0; s < MAX_UNROLLED_SPLITS; ++s)
+        if (s < a.splits) part[s] = *reinterpret_cast<const float4*>(src + s * a.split_stride);
+    float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll
+    for (int s = 0; s < MAX_UNROLLED_SPLITS; ++s)
+        if (s < a.splits) add4(v, part[s]);
+    if (a.bias) add4(v, *reinterpret_cast<const float4*>(a.bias + i));
+    const int q_width = a.heads * a.head_dim, k_width = a.kv_heads * a.head_dim, v_width = a.kv_heads * a.value_dim;
+    if (i < q_width) {
+        store4(static_cast<OutT*>(a.q_out) + static_cast<size_t>(token) * q_width + i, v);
+    } else if (i < q_width + k_width + v_width) {
+        const bool is_k = i < q_width + k_width;
+        const int column = is_k ? i - q_width : i - q_width - k_width;
+        const int dim = is_k ? a.head_dim : a.value_dim;
+        const int head = column / dim, e = column - head * dim;
+        if (a.slot_mapping) {
+            const int slot = a.slot_mapping[token];
+            if (slot < 0) return;
+            const size_t page = slot / a.page_size, offset = slot % a.page_size;
+            OutT* pages = static_cast<OutT*>(is_k ? a.k_pages : a.v_pages);
+            store4(pages + ((page * a.kv_heads + head) * a.page_size + offset) * dim + e, v);
+        } else {
+            OutT* dense = static_cast<OutT*>(is_k ? a.k_dense : a.v_dense);
+            store4(dense + static_cast<size_t>(token) * (is_k ? k_width : v_width) + column, v);
+        }
+    } else {
+        const int g = i - q_width - k_width - v_width;
+        if (g < a.gates)
+            store4(a.gate_out + static_cast<size_t>(token) * a.gates + g,
+                   make_float4(1.0f / (1.0f + expf(-v.x)), 1.0f / (1.0f + expf(-v.y)), 1.0f / (1.0f + expf(-v.z)), 1.0f / (1.0f + expf(-v.w))));
+    }
+}
+
 ME_EXPORT int me_qk_wide_norm_rope_store(const float* qkv, int splits, long long split_stride, int row_width,
                                          const float* q_weight, const float* k_weight, float eps, const float* cos_sin,
                                          const int* slot_mapping, void* q_out, void* k_pages, void* v_pages,
@@ -1036,6 +1209,16 @@ ME_EXPORT int me_qk_wide_norm_rope_store(const float* qkv, int splits, long long
     WideQkvArgs a{qkv, splits, (size_t)split_stride, row_width, q_weight, k_weight, eps, reinterpret_cast<const float2*>(cos_sin),
                   slot_mapping, q_out, k_pages, v_pages, k_dense, v_dense, gate_out, tokens, heads, kv_heads, head_dim,
                   value_dim, page_size, rotary_dim, gates, bias};
+    // Which kernel runs follows from the layer (no norm, no rotation, sizes in fours) and the engine's buffers alone.
+    const bool alone = q_weight == nullptr && k_weight == nullptr && cos_sin == nullptr && splits <= MAX_UNROLLED_SPLITS &&
+                       head_dim % 4 == 0 && value_dim % 4 == 0 && gates % 4 == 0 && row_width % 4 == 0 && split_stride % 4 == 0 &&
+                       aligned16(qkv) && aligned16(bias) && aligned16(q_out) && aligned16(gate_out) &&
+                       aligned16(k_pages) && aligned16(v_pages) && aligned16(k_dense) && aligned16(v_dense);
+    if (alone) {
+        const dim3 grid((row_width / 4 + 255) / 256, tokens);
+        if (out_type == ME_BF16) return launch_kernel(qkv_bias_store_kernel<__nv_bfloat16>, grid, 256, 0, stream, a);
+        return launch_kernel(qkv_bias_store_kernel<float>, grid, 256, 0, stream, a);
+    }
     if (out_type == ME_BF16) {
         auto kernel = qk_wide_norm_rope_store_kernel<__nv_bfloat16>;
         if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);

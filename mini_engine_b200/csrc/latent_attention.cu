@@ -47,7 +47,17 @@ __global__ void __launch_bounds__(256) latent_down_finish_kernel(DownArgs a) {
     float q_sq = 0.0f, c_sq = 0.0f;
     for (int i = threadIdx.x; i < a.row_width; i += 256) {
         float v = 0.0f;
-        for (int s = 0; s < a.splits; ++s) v += src[s * a.split_stride + i];
+        if (a.splits <= 8) {  // all loads of the column first, then the sum in the same ascending order
+            float part[8];
+#pragma unroll
+            for (int s = 0; s < 8; ++s)
+                if (s < a.splits) part[s] = src[s * a.split_stride + i];
+#pragma unroll
+            for (int s = 0; s < 8; ++s)
+                if (s < a.splits) v += part[s];
+        } else {
+            for (int s = 0; s < a.splits; ++s) v += src[s * a.split_stride + i];
+        }
         row[i] = v;
         if (i < a.q_rank) q_sq = fmaf(v, v, q_sq);
         else if (i < a.q_rank + a.kv_rank) c_sq = fmaf(v, v, c_sq);

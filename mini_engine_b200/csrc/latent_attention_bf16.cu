@@ -14,7 +14,7 @@
 //
 // Scores, maxima, sums and the output accumulate in float32.  Keys outside the visible range are zero-filled in
 // shared memory and never read from the cache.  Requests that bring one token split their keys over several CTAs
-// (spans of 256 keys by absolute position, so the split depends on the position only); each writes a partial
+// (spans of 128 keys by absolute position, so the split depends on the position only); each writes a partial
 // (maximum, sum, unnormalised output) and the CTA that arrives last merges them in ascending key order.
 //
 // head_product_bf16: out[t][h][n] = sum_k x[t][h][k] W[h][k][n] on the same instructions: a CTA takes 64 tokens of
@@ -25,7 +25,7 @@
 constexpr int LAT_ROWS = 32;      // (token, head) pairs per CTA
 constexpr int LAT_KEYS = 64;      // keys per tile
 constexpr int LAT_THREADS = 256;  // eight warps
-constexpr int LAT_SPAN = 256;     // keys of one CTA of a split request
+constexpr int LAT_SPAN = 128;     // keys of one CTA of a split request
 constexpr float LAT_LOG2E = 1.4426950408889634f;
 constexpr int LAT_MAX_SMEM = 226 * 1024;  // dynamic shared memory a CTA may ask for (the kernel has a few static bytes too)
 
@@ -288,6 +288,58 @@ __global__ void __launch_bounds__(LAT_THREADS, 1) latent_attention_kernel(Latent
     __syncthreads();
     if (!is_last) return;
     __threadfence();
+    // Each row's weights first (a warp per row: exp2(maximum of the partial - maximum of all), zero for a partial that
+    // saw no key, and the weighted sums added in ascending order by one lane), into the shared memory that held the
+    // tiles; then every output element is one pass over the partials with nothing to wait for but its own loads.
+    const int capacity = (LAT_ROWS + 2 * LAT_KEYS) * p.width / 2;  // floats of the query and key tiles
+    if (LAT_ROWS * (2 * active + 1) <= capacity) {
+        float* weights = reinterpret_cast<float*>(smem);    // [32][active]
+        float* weighted = weights + LAT_ROWS * active;      // [32][active] weight * sum of the partial
+        float* totals = weighted + LAT_ROWS * active;       // [32]
+        for (int row = warp; row < rows_valid; row += LAT_THREADS / 32) {
+            const float* part = p.partials + (static_cast<size_t>(entry) * p.heads + row0 + row) * p.max_splits * STRIDE;
+            float total_max = -INFINITY;
+            for (int sl = lane; sl < active; sl += 32) total_max = fmaxf(total_max, __ldcg(part + sl * STRIDE + R));
+#pragma unroll
+            for (int d = 16; d > 0; d >>= 1) total_max = fmaxf(total_max, __shfl_xor_sync(0xffffffffu, total_max, d));
+            for (int sl = lane; sl < active; sl += 32) {
+                const float m = __ldcg(part + sl * STRIDE + R);
+                const float weight = m == -INFINITY ? 0.0f : exp2f(m - total_max);
+                weights[row * active + sl] = weight;
+                weighted[row * active + sl] = __ldcg(part + sl * STRIDE + R + 1) * weight;
+            }
+            __syncwarp();
+            if (lane == 0) {
+                float total = 0.0f;
+                for (int sl = 0; sl < active; ++sl) total += weighted[row * active + sl];
+                totals[row] = total;
+            }
+        }
+        __syncthreads();
+        for (int idx = threadIdx.x; idx < rows_valid * (R / 2); idx += LAT_THREADS) {
+            const int row = idx / (R / 2), col = (idx - row * (R / 2)) * 2;
+            const size_t pair_index = static_cast<size_t>(token0) * p.heads + row0 + row;
+            const float* part = p.partials + (static_cast<size_t>(entry) * p.heads + row0 + row) * p.max_splits * STRIDE + col;
+            const float* weight = weights + row * active;
+            float2 value = make_float2(0.0f, 0.0f);
+            int sl = 0;
+            for (; sl + 4 <= active; sl += 4) {
+                float2 v[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) v[j] = __ldcg(reinterpret_cast<const float2*>(part + (sl + j) * STRIDE));
+#pragma unroll
+                for (int j = 0; j < 4; ++j) value.x = fmaf(v[j].x, weight[sl + j], value.x), value.y = fmaf(v[j].y, weight[sl + j], value.y);
+            }
+            for (; sl < active; ++sl) {
+                const float2 v = __ldcg(reinterpret_cast<const float2*>(part + sl * STRIDE));
+                value.x = fmaf(v.x, weight[sl], value.x), value.y = fmaf(v.y, weight[sl], value.y);
+            }
+            const float whole = (p.gate ? p.gate[pair_index] : 1.0f) / totals[row];
+            *reinterpret_cast<uint32_t*>(p.out + pair_index * R + col) = pack_bf16(value.x * whole, value.y * whole);
+        }
+        return;
+    }
+    // more partials than the shared memory holds weights for: every element finds its weights itself
     for (int idx = threadIdx.x; idx < rows_valid * R; idx += LAT_THREADS) {
         const int row = idx / R, col = idx - row * R;
         const size_t pair_index = static_cast<size_t>(token0) * p.heads + row0 + row;

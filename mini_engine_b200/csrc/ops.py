@@ -531,7 +531,7 @@ def paged_attention(
     )  # fmt: skip
 
 
-LATENT_ROWS, LATENT_SPAN = 32, 256  # (token, head) pairs of a CTA of the kernel below; keys of a CTA of a split request
+LATENT_ROWS, LATENT_SPAN = 32, 128  # (token, head) pairs of a CTA of the kernel below; keys of a CTA of a split request
 
 
 def latent_attention_supports(width: int, rank: int | None, kv_heads: int = 1) -> bool:
