@@ -4,9 +4,10 @@
   (scratch for the partial results comes from the workspace): with groups of at most 8 heads and
   pages of a power of two of at least 8 keys the one that fetches whole page rows by TMA, else
   the one that gathers keys row by row;
-* otherwise, head size 128, no window, pages of 8 to 128 tokens and a portion of at least 32
-  tokens in the batch: the tcgen05 kernel (both products on the tensor cores with accumulators in
-  tensor memory, keys and values fetched by TMA page by page);
+* otherwise, head size 128, pages of 8 to 128 tokens and a portion of at least 32 tokens in the
+  batch: the tcgen05 kernel (both products on the tensor cores with accumulators in tensor memory,
+  keys and values fetched by TMA page by page; with a window, a distance bias, a silent participant
+  or a gate, its form of one query head per CTA that knows them);
 * otherwise: the mma.sync portions kernel, for any mix of portion lengths.
 
 Head sizes 64 and 128 are taken; other sizes use the generic kernel.
@@ -40,7 +41,7 @@ def _tc_library():
         import ctypes
 
         lib = load_library("attention_tcgen05")
-        lib.me_attention_tcgen05.argtypes = [c_void_p] * 7 + [c_float] + [c_int] * 7 + [c_void_p, c_void_p]
+        lib.me_attention_tcgen05.argtypes = [c_void_p] * 7 + [c_float] + [c_int] * 7 + [c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p]
         lib.me_attention_tcgen05.restype = c_int
         lib.me_attention_take_error.argtypes = [ctypes.POINTER(c_int)]
         lib.me_attention_take_error.restype = c_int
@@ -99,7 +100,7 @@ def _query_map(q: torch.Tensor):
 def tensor_memory_kernel_takes(head_dim: int, page_size: int, window: int, max_query_len: int) -> bool:
     return (
         head_dim == 128
-        and window == 0
+        and window >= 0
         and 8 <= page_size <= 128
         and 128 % page_size == 0
         and max_query_len >= TENSOR_MEMORY_MIN_TOKENS
@@ -197,8 +198,7 @@ def paged_attention(q, k_pages, v_pages, block_table, ctx, out, heads, kv_heads,
     ``sink``: the softmax has one more participant of score zero and no value, or of the learned score
     ``sink_values[h]`` (float32 ``[heads]``); ``gate`` (float32 ``[T, heads]`` or ``[T, heads * head_dim]``): a
     multiplier on every head's output, or on every element; ``slopes`` (float32 ``[heads]``): ``slopes[h] * (p - j)``
-    is taken off the scaled score of query ``p`` and key ``j``.  All are known to the mma.sync kernels, so with any of
-    them a prompt portion takes the portions kernel where it would otherwise take the tcgen05 kernel."""
+    is taken off the scaled score of query ``p`` and key ``j``.  Every kernel knows all of them."""
     for name, t in (("q", q), ("out", out), ("k_pages", k_pages), ("v_pages", v_pages)):
         if t.dtype != torch.bfloat16 or not t.is_contiguous():
             raise ops.KernelError(f"{name} must be contiguous bfloat16")
@@ -256,10 +256,10 @@ def paged_attention(q, k_pages, v_pages, block_table, ctx, out, heads, kv_heads,
                 head_dim, page_size, width, window, ids_ptr, *options, stream,
             )  # fmt: skip
             ops._check(code, "attention_decode_bf16")
-        elif not sink_flag and gate is None and slopes is None and tensor_memory_kernel_takes(head_dim, page_size, window, longest):
+        elif tensor_memory_kernel_takes(head_dim, page_size, window, longest):
             code = _tc_library().me_attention_tcgen05(
                 _query_map(q), _page_map(k_pages), _page_map(v_pages), *common[3:], scale, entries, longest, heads,
-                kv_heads, head_dim, page_size, width, ids_ptr, stream,
+                kv_heads, head_dim, page_size, width, ids_ptr, window, *options, stream,
             )  # fmt: skip
             ops._check(code, "attention_tcgen05")
         else:

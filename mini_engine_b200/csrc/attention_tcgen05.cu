@@ -30,7 +30,9 @@
 //
 // Formula and conventions as in attention_bf16.cu (YuvGev00/mini-engine:
 // src/mini_engine/attention.py:84-86,160-175; probabilities rounded to the value dtype before the
-// second product, :173).  head_dim is 128; pages of 8 to 128 tokens; no window.
+// second product, :173).  head_dim is 128; pages of 8 to 128 tokens.  The form of one query head per CTA also
+// takes a sliding window, a linear distance bias, a silent participant of the softmax and a gate on the output
+// (attention_tcgen05_kernel<true>); the form of two heads per CTA takes none of them.
 #include "tcgen05.cuh"
 
 constexpr int TC_ROWS = 128;   // query rows per CTA
@@ -52,6 +54,13 @@ struct TcAttnParams {
     __nv_bfloat16* out;       // [tokens][heads][128]
     float scale_log2;
     int heads, kv_heads, page_size, table_width;
+    // The options of attention_tcgen05_kernel<true>:
+    int window;                // query p sees keys (p - window, p]; 0: all keys up to p
+    int sink;                  // the softmax has one more participant without a value
+    int gate_width;            // 1: a gate per (token, head); 128: a gate per output element
+    const float* slopes;       // [heads] slope_h * (p - j) is taken off the scaled score, or null
+    const float* sink_values;  // [heads] the silent participant's score (null with `sink`: zero)
+    const float* gate;         // [tokens][heads * gate_width] multiplier of the output, or null
 };
 
 // 2^x by the special-function unit alone (about 2 ulp; the result is rounded to bfloat16 anyway).
@@ -122,6 +131,11 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
     return packed;
 }
 
+// OPT: the kernel also knows a sliding window (tiles wholly behind the window of the block's first row are never
+// fetched; the edge tiles are masked element by element), a linear distance bias, a silent participant in the
+// softmax's denominator and a multiplier on the output.  Scaled, biased scores and the mask are formed before the
+// row's maximum is taken, so the maximum is that of the values whose exponentials are summed.
+template <bool OPT>
 __global__ void __launch_bounds__(TC_THREADS, 2)
 attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                          const __grid_constant__ CUtensorMap map_v, TcAttnParams p) {
@@ -170,7 +184,9 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     const int context = p.context_lens[entry];
     const int rows_valid = min(TC_ROWS, new_tokens - q_block * TC_ROWS);
     const int pos0 = context - new_tokens + q_block * TC_ROWS;  // position of row 0
-    const int tiles_count = has_work ? (pos0 + rows_valid - 1) / TC_KEYS + 1 : 0;
+    const int lowest = (OPT && p.window > 0) ? max(pos0 - p.window + 1, 0) : 0;  // the first key that row 0 sees
+    const int first_tile = lowest / TC_KEYS;
+    const int tiles_count = has_work ? (pos0 + rows_valid - 1) / TC_KEYS + 1 - first_tile : 0;
 
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
@@ -188,11 +204,14 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                 tma_load_2d(q_tile + TC_HALF_BYTES, &map_q, head * TC_DIM + 64, token0 + q_block * TC_ROWS, q_full);
             }
             const bool loads = lane < pages_per_tile;
-            int page = loads ? table[min(lane, last_page_index)] : 0;
+            // Pages wholly behind the window may have been given back: a tile's page indices are held inside
+            // [the page of the first visible key, the page of the last key]; what a row must not see is masked.
+            const int first_page_index = lowest / p.page_size;
+            int page = loads ? table[min(max(first_tile * pages_per_tile + lane, first_page_index), last_page_index)] : 0;
             bool ok = true;
             for (int j = 0; j < tiles_count && ok; ++j) {
                 const uint32_t parity = j & 1;
-                const int next_page = (loads && j + 1 < tiles_count) ? table[min((j + 1) * pages_per_tile + lane, last_page_index)] : 0;
+                const int next_page = (loads && j + 1 < tiles_count) ? table[min(max((first_tile + j + 1) * pages_per_tile + lane, first_page_index), last_page_index)] : 0;
                 const int row = (page * p.kv_heads + kv_head) * p.page_size;
                 for (int which = 0; which < 2 && ok; ++which) {  // keys, then values
                     uint64_t* empty = which ? v_empty : k_empty;
@@ -257,6 +276,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
         const int col0 = half * 64;
         float row_max = -INFINITY, row_sum = 0.0f;  // the maximum of the whole row; the sum of this thread's columns
+        const float slope_log2 = (OPT && p.slopes) ? p.slopes[head] * TC_LOG2E : 0.0f;
         // A wait that ran out must not leave other threads at a named barrier: a thread that saw
         // one keeps walking to the next barrier, where all 256 learn of it and leave together.
         bool ok = true;
@@ -265,10 +285,12 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             const uint32_t parity = j & 1;
             ok = ok && mbar_wait(s_full, parity);
             tcgen05_fence_after();
-            const int first_key = j * TC_KEYS + col0;
-            // Only the last tile or two of a block hold keys that some row must not see; every other
-            // tile takes the path without per-element position tests.
-            const bool masked_tile = j * TC_KEYS + TC_KEYS - 1 > pos0;
+            const int tile = first_tile + j;
+            const int first_key = tile * TC_KEYS + col0;
+            // Only the last tile or two of a block hold keys that some row must not see (and, with a window, the
+            // first one or two); every other tile takes the path without per-element position tests.
+            const bool masked_tile = tile * TC_KEYS + TC_KEYS - 1 > pos0 ||
+                                     (OPT && p.window > 0 && tile * TC_KEYS < pos0 + TC_ROWS - p.window);
             uint32_t raw[64];
             tcgen05_ld32_nowait(tmem_s + lane_base + col0, raw);
             tcgen05_ld32_nowait(tmem_s + lane_base + col0 + 32, raw + 32);
@@ -276,7 +298,24 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             tcgen05_pin32(raw);
             tcgen05_pin32(raw + 32);
             float best[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};  // four chains, not one of 64 links
-            if (masked_tile) {
+            if (OPT) {
+                // raw <- score * scale + slope * (key - position), in the exponent's base 2; -inf where masked
+                const float2 scale2 = make_float2(p.scale_log2, p.scale_log2), slope2 = make_float2(slope_log2, slope_log2);
+                float2 distance = make_float2(static_cast<float>(first_key - row_pos), static_cast<float>(first_key + 1 - row_pos));
+                const int lowest_seen = p.window > 0 ? row_pos - p.window + 1 : 0;
+#pragma unroll
+                for (int i = 0; i < 64; i += 2) {
+                    float2 x = __ffma2_rn(make_float2(__uint_as_float(raw[i]), __uint_as_float(raw[i + 1])), scale2, __fmul2_rn(slope2, distance));
+                    distance = __fadd2_rn(distance, make_float2(2.0f, 2.0f));
+                    if (masked_tile) {
+                        const int key = first_key + i;
+                        if (key > row_pos || key < lowest_seen) x.x = -INFINITY;
+                        if (key + 1 > row_pos || key + 1 < lowest_seen) x.y = -INFINITY;
+                    }
+                    raw[i] = __float_as_uint(x.x), raw[i + 1] = __float_as_uint(x.y);
+                    best[(i >> 1) & 3] = fmax3(best[(i >> 1) & 3], x.x, x.y);
+                }
+            } else if (masked_tile) {
 #pragma unroll
                 for (int i = 0; i < 64; ++i)
                     if (first_key + i <= row_pos) best[i & 3] = fmaxf(best[i & 3], __uint_as_float(raw[i]));
@@ -291,7 +330,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             float* slot = exchange + parity * 256;
             slot[half * 128 + row] = tile_max;
             if (softmax_barrier_any(!ok)) break;
-            tile_max = fmaxf(tile_max, slot[(half ^ 1) * 128 + row]) * p.scale_log2;  // the scale is positive
+            tile_max = fmaxf(tile_max, slot[(half ^ 1) * 128 + row]) * (OPT ? 1.0f : p.scale_log2);  // the scale is positive
             // The row's reference value `row_max` follows its true maximum lazily: only when the
             // maximum of some row of the warp has grown by more than 2^8 is O rescaled (and the
             // second product of the tile before waited for); until then probabilities are taken
@@ -304,7 +343,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             } else if (__any_sync(0xffffffffu, new_max - row_max > 8.0f)) {
                 ok = ok && mbar_wait(o_full + ((j - 1) & 1), ((j - 1) >> 1) & 1);  // the MMAs run in order: all of O is complete
                 tcgen05_fence_after();
-                const float rescale = exp2f(row_max - new_max);
+                // (with a window a row may have seen no key yet: its sum and output are zero and stay so)
+                const float rescale = (OPT && row_max == -INFINITY) ? 1.0f : exp2f(row_max - new_max);
                 row_sum *= rescale;
                 row_max = new_max;
 #pragma unroll 1
@@ -325,7 +365,15 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
 #pragma unroll
             for (int c = 0; c < 2; ++c) {
                 uint32_t packed[16];
-                if (masked_tile) {
+                if (OPT) {
+#pragma unroll
+                    for (int i = 0; i < 32; i += 2) {
+                        const float2 x = __fadd2_rn(make_float2(__uint_as_float(raw[c * 32 + i]), __uint_as_float(raw[c * 32 + i + 1])), base2);
+                        const float2 pr = make_float2(fast_exp2(x.x), fast_exp2(x.y));  // 2^-inf = 0
+                        partial[(i >> 1) & 1] = __fadd2_rn(partial[(i >> 1) & 1], pr);
+                        packed[i / 2] = pack_bf16x2(pr.x, pr.y);
+                    }
+                } else if (masked_tile) {
 #pragma unroll
                     for (int i = 0; i < 32; i += 2) {
                         const int key = first_key + c * 32 + i;
@@ -360,14 +408,27 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         ok = !softmax_barrier_any(!ok || j < tiles_count);
         if (!ok && threadIdx.x == 64) atomicCAS(&g_attention_error, 0, 3 << 8);
         row_sum += slot[(half ^ 1) * 128 + row];
+        if (OPT && p.sink)  // both threads of the row hold the same reference value
+            row_sum += exp2f((p.sink_values ? p.sink_values[head] * TC_LOG2E : 0.0f) - (row_max == -INFINITY ? 0.0f : row_max));
         if (ok) {
             tcgen05_fence_after();
-            const float inv = 1.0f / row_sum;
-            __nv_bfloat16* dst = p.out + (static_cast<size_t>(token0 + q_block * TC_ROWS + row) * p.heads + head) * TC_DIM + col0;
+            float inv = 1.0f / row_sum;
+            const size_t pair_index = static_cast<size_t>(token0 + q_block * TC_ROWS + row) * p.heads + head;
+            const bool element_gates = OPT && p.gate != nullptr && p.gate_width > 1;
+            if (OPT && p.gate != nullptr && p.gate_width == 1 && row < rows_valid) inv *= p.gate[pair_index];
+            const float* gate_row = p.gate + pair_index * TC_DIM + col0;
+            __nv_bfloat16* dst = p.out + pair_index * TC_DIM + col0;
 #pragma unroll 1
             for (int c = 0; c < 2; ++c) {
                 float o[32];
                 tcgen05_ld32(tmem_o + lane_base + col0 + c * 32, o);  // collective: every lane takes part
+                if (element_gates && row < rows_valid) {
+#pragma unroll
+                    for (int i = 0; i < 32; i += 4) {
+                        const float4 g = *reinterpret_cast<const float4*>(gate_row + c * 32 + i);
+                        o[i] *= g.x, o[i + 1] *= g.y, o[i + 2] *= g.z, o[i + 3] *= g.w;
+                    }
+                }
                 if (row < rows_valid) {
 #pragma unroll
                     for (int i = 0; i < 32; i += 8) {
@@ -734,8 +795,10 @@ attention_tcgen05_duo_kernel(const __grid_constant__ CUtensorMap map_q, const __
 ME_EXPORT int me_attention_tcgen05(const void* map_q, const void* map_k, const void* map_v, const int* block_table,
                                    const int* cu_tokens, const int* context_lens, void* out, float scale, int entries,
                                    int max_new_tokens, int heads, int kv_heads, int head_dim, int page_size,
-                                   int table_width, const int* entry_ids, cudaStream_t stream) {
+                                   int table_width, const int* entry_ids, int window, int sink, const float* gate,
+                                   int gate_width, const float* slopes, const float* sink_values, cudaStream_t stream) {
     if (entries <= 0) return 0;
+    if (window < 0 || (gate != nullptr && gate_width != 1 && gate_width != TC_DIM)) return ME_ERR_ARGUMENT;
     if (head_dim != TC_DIM || kv_heads < 1 || heads % kv_heads) return ME_ERR_UNSUPPORTED;
     if (page_size < 8 || page_size > TC_KEYS || TC_KEYS % page_size) return ME_ERR_UNSUPPORTED;
     alignas(64) CUtensorMap q, k, v;
@@ -743,18 +806,23 @@ ME_EXPORT int me_attention_tcgen05(const void* map_q, const void* map_k, const v
     memcpy(&k, map_k, sizeof(k));
     memcpy(&v, map_v, sizeof(v));
     TcAttnParams p{block_table, cu_tokens, context_lens, entry_ids, static_cast<__nv_bfloat16*>(out), scale * TC_LOG2E,
-                   heads, kv_heads, page_size, table_width};
+                   heads, kv_heads, page_size, table_width, window, (sink || sink_values) ? 1 : 0, gate_width, slopes, sink_values, gate};
     const int blocks = (max_new_tokens + TC_ROWS - 1) / TC_ROWS;
+    constexpr int SMEM = 6 * TC_HALF_BYTES + 1024 + 256 + 2 * 2 * 128 * 4;
+    if (window > 0 || p.sink || gate != nullptr || slopes != nullptr) {
+        static SharedMemoryOptIn with_options;
+        if (const int e = with_options(attention_tcgen05_kernel<true>, SMEM)) return e;
+        return launch_kernel(attention_tcgen05_kernel<true>, dim3(heads, blocks, entries), TC_THREADS, SMEM, stream, q, k, v, p);
+    }
     if ((heads / kv_heads) % 2 == 0) {  // two query heads of a KV group per CTA
         static SharedMemoryOptIn duo_opt_in;
         if (const int e = duo_opt_in(attention_tcgen05_duo_kernel, DUO_SMEM_BYTES)) return e;
         return launch_kernel(attention_tcgen05_duo_kernel, dim3(heads / 2, blocks, entries), DUO_THREADS, DUO_SMEM_BYTES,
                              stream, q, k, v, p);
     }
-    constexpr int SMEM = 6 * TC_HALF_BYTES + 1024 + 256 + 2 * 2 * 128 * 4;
     static SharedMemoryOptIn opt_in;
-    if (const int e = opt_in(attention_tcgen05_kernel, SMEM)) return e;
-    return launch_kernel(attention_tcgen05_kernel, dim3(heads, blocks, entries), TC_THREADS, SMEM, stream, q, k, v, p);
+    if (const int e = opt_in(attention_tcgen05_kernel<false>, SMEM)) return e;
+    return launch_kernel(attention_tcgen05_kernel<false>, dim3(heads, blocks, entries), TC_THREADS, SMEM, stream, q, k, v, p);
 }
 
 ME_EXPORT int me_attention_take_error(int* code) {

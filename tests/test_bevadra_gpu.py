@@ -536,6 +536,68 @@ def test_tensor_core_attention_with_bias_sinks_and_element_gates(head_dim, heads
     assert error < 2e-2, f"relative error {error:.3g}"
 
 
+@pytest.mark.parametrize("heads,kv_heads,page", [(4, 2, 8), (6, 2, 16), (3, 1, 32), (2, 2, 128)])
+@pytest.mark.parametrize("news", [[400, 90, 130, 300], [129, 33, 128, 2], [257, 1, 40, 256]])
+@pytest.mark.parametrize(
+    "which,window",
+    [("all", w) for w in (0, 1, 70, 128, 200, 257)] + [("window_only", w) for w in (1, 70, 128, 200, 257)]
+    + [(one, w) for one in ("bias", "sink", "gate_per_head") for w in (0, 200)],
+)  # fmt: skip
+def test_tensor_memory_attention_with_a_window_and_the_options(heads, kv_heads, page, news, window, which):
+    """Prompt portions of 32 tokens and more with heads of 128 run with both products on tcgen05: windows that end
+    inside, at the edge of and several tiles behind a block's first row, each option alone and all together, pages
+    behind the window given back (their table entries are -1 and their contents large numbers), against float64."""
+    from test_kernels_gpu import fake_context
+
+    from mini_engine_b200.csrc import attention_bf16, ops
+
+    head_dim = 128
+    g = torch.Generator().manual_seed(heads + page + len(news) + window + news[0])
+    lengths = [400, 90, 130, 300]
+    total_pages = sum(-(-n // page) for n in lengths) + 3
+    order = torch.randperm(total_pages, generator=g).tolist()
+    k_pages = torch.full((total_pages, kv_heads, page, head_dim), 3e4).to(torch.bfloat16)
+    v_pages = torch.full((total_pages, kv_heads, page, head_dim), -3e4).to(torch.bfloat16)
+    table = torch.full((len(lengths), max(-(-n // page) for n in lengths) + 1), -1, dtype=torch.int32)
+    slopes = 20.0 * slopes_of(heads) if which in ("all", "bias") else None
+    sink = 3.0 * torch.randn(heads, generator=g) if which in ("all", "sink") else None
+    q_rows, want_rows, gate_rows, entry_of, positions = [], [], [], [], []
+    for b, (n, new) in enumerate(zip(lengths, news)):
+        q = (0.5 * torch.randn(n, heads, head_dim, generator=g)).to(torch.bfloat16)
+        k = torch.randn(n, kv_heads, head_dim, generator=g).to(torch.bfloat16)
+        v = torch.randn(n, kv_heads, head_dim, generator=g).to(torch.bfloat16)
+        gate = {"all": torch.rand(n, heads * head_dim, generator=g), "gate_per_head": torch.rand(n, heads, generator=g)}.get(which)
+        first_needed = max(0, n - new - window + 1) if window else 0
+        for i in range(first_needed // page, -(-n // page)):
+            table[b, i] = order.pop()
+        for p in range((first_needed // page) * page, n):
+            k_pages[table[b, p // page], :, p % page] = k[p]
+            v_pages[table[b, p // page], :, p % page] = v[p]
+        wide = None if gate is None else (gate if which == "all" else gate.repeat_interleave(head_dim, dim=1))
+        want = plain_biased_attention(q.double(), k.double(), v.double(), head_dim**-0.5, window or None, slopes, sink, wide)
+        q_rows.append(q[n - new :]), want_rows.append(want[n - new :])
+        if gate is not None:
+            gate_rows.append(gate[n - new :])
+        entry_of += [b] * new
+        positions += list(range(n - new, n))
+    data = dict(new_counts=news, lengths=lengths, entry_of=torch.tensor(entry_of, dtype=torch.int32).cuda(),
+                positions=torch.tensor(positions, dtype=torch.int32).cuda())  # fmt: skip
+    q_all = torch.cat(q_rows).reshape(-1, heads * head_dim).contiguous().cuda()
+    want = torch.cat(want_rows).reshape(-1, heads * head_dim).float()
+    out = torch.full_like(q_all, float("nan"))
+    assert attention_bf16.tensor_memory_kernel_takes(head_dim, page, window, max(news))
+    ops.paged_attention(
+        q=q_all, k_pages=k_pages.cuda(), v_pages=v_pages.cuda(), block_table=table.cuda(), ctx=fake_context(data), out=out,
+        heads=heads, kv_heads=kv_heads, head_dim=head_dim, scale=head_dim**-0.5, window=window,
+        gate=torch.cat(gate_rows).contiguous().cuda() if gate_rows else None,
+        slopes=None if slopes is None else slopes.cuda(), sink_values=None if sink is None else sink.cuda(),
+    )  # fmt: skip
+    torch.cuda.synchronize()
+    assert attention_bf16.take_error() == 0
+    error = float((out.float().cpu() - want).abs().max()) / float(want.abs().max())
+    assert error < 2e-2, f"relative error {error:.3g}"
+
+
 @pytest.mark.parametrize("rank,rot", [(128, 64), (256, 64), (512, 64), (384, 0)])
 @pytest.mark.parametrize("heads,page", [(5, 4), (16, 16), (40, 16)])
 @pytest.mark.parametrize("news", [[1, 1, 1, 1], [90, 5, 130, 2], [1, 40, 1, 7]])
