@@ -419,21 +419,26 @@ struct HeadProductParams {
     const float2* cos_sin;        // [tokens][rotary_dim / 2] or null
     __nv_bfloat16* out;           // [tokens][heads][outs + tail]
     int tokens, heads, inner, outs, tail, rotary_dim;
+    int chunks_per_cta;  // consecutive output chunks of 128 that one CTA walks with the same x tile
 };
 
-// grid (token tiles, heads, output chunks of 128).
+// grid (token tiles, heads, groups of output chunks of 128).
 template <bool FLOAT_IN>
 __global__ void __launch_bounds__(HPT_THREADS) head_product_bf16_kernel(HeadProductParams a) {
     extern __shared__ __align__(128) uint8_t smem[];
     __nv_bfloat16* x_tile = reinterpret_cast<__nv_bfloat16*>(smem);  // [64][inner]
     __nv_bfloat16* w_slabs = x_tile + HPT_TOKENS * a.inner;          // [2 stages][64 k][128 outputs]
-    const int head = blockIdx.y, first = blockIdx.x * HPT_TOKENS, n0 = blockIdx.z * HPT_OUTS;
+    const int head = blockIdx.y, first = blockIdx.x * HPT_TOKENS;
+    const int chunk0 = blockIdx.z * a.chunks_per_cta;
+    const int my_chunks = min(a.chunks_per_cta, (a.outs + HPT_OUTS - 1) / HPT_OUTS - chunk0);
+    const int slabs = a.inner / HPT_SLAB;
     const int count = min(HPT_TOKENS, a.tokens - first);
     const int in_head = a.inner + a.tail, out_head = a.outs + a.tail;
     const int chunks = a.inner / 8;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const __nv_bfloat16* weight = a.weight + static_cast<size_t>(head) * a.inner * a.outs;
-    auto fetch_slab = [&](int slab, int stage) {
+    auto fetch_slab = [&](int item, int stage) {  // item: (output chunk, slab) in the order they are used
+        const int n0 = (chunk0 + item / slabs) * HPT_OUTS, slab = item % slabs;
         __nv_bfloat16* dst = w_slabs + stage * HPT_SLAB * HPT_OUTS;
         for (int idx = threadIdx.x; idx < HPT_SLAB * (HPT_OUTS / 8); idx += HPT_THREADS) {
             const int k = idx / (HPT_OUTS / 8), chunk = idx % (HPT_OUTS / 8);
@@ -447,7 +452,30 @@ __global__ void __launch_bounds__(HPT_THREADS) head_product_bf16_kernel(HeadProd
     cp_async_commit();
     pdl_wait();
     // x of this head -> shared memory as bfloat16 (rows past the end are zero)
-    for (int idx = threadIdx.x; idx < HPT_TOKENS * chunks; idx += HPT_THREADS) {
+    int x_done = 0;
+    if (FLOAT_IN && a.splits == 1) {  // whole sums: four chunks of eight per thread with all their loads in flight
+        for (; x_done + 4 * HPT_THREADS <= HPT_TOKENS * chunks; x_done += 4 * HPT_THREADS) {
+            float4 lo[4], hi[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int idx = x_done + u * HPT_THREADS + threadIdx.x;
+                const int t = idx / chunks, chunk = idx - t * chunks;
+                lo[u] = hi[u] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                if (t < count) {
+                    const float* src = static_cast<const float*>(a.in) + (static_cast<size_t>(first + t) * a.heads + head) * in_head + chunk * 8;
+                    lo[u] = *reinterpret_cast<const float4*>(src), hi[u] = *reinterpret_cast<const float4*>(src + 4);
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int idx = x_done + u * HPT_THREADS + threadIdx.x;
+                const int t = idx / chunks, chunk = idx - t * chunks;
+                *reinterpret_cast<uint4*>(x_tile + swizzled_at(t, chunk, chunks) * 8) =
+                    make_uint4(pack_bf16(lo[u].x, lo[u].y), pack_bf16(lo[u].z, lo[u].w), pack_bf16(hi[u].x, hi[u].y), pack_bf16(hi[u].z, hi[u].w));
+            }
+        }
+    }
+    for (int idx = x_done + threadIdx.x; idx < HPT_TOKENS * chunks; idx += HPT_THREADS) {
         const int t = idx / chunks, chunk = idx - t * chunks;
         __nv_bfloat16* dst = x_tile + swizzled_at(t, chunk, chunks) * 8;
         const size_t at = (static_cast<size_t>(first + t) * a.heads + head) * in_head + chunk * 8;
@@ -473,11 +501,11 @@ __global__ void __launch_bounds__(HPT_THREADS) head_product_bf16_kernel(HeadProd
     for (int n = 0; n < HPT_OUTS / 8; ++n)
 #pragma unroll
         for (int i = 0; i < 4; ++i) acc[n][i] = 0.0f;
-    const int slabs = a.inner / HPT_SLAB;
-    for (int slab = 0; slab < slabs; ++slab) {
-        const int stage = slab & 1;
-        if (slab + 1 < slabs) {
-            fetch_slab(slab + 1, stage ^ 1);
+    const int items = my_chunks * slabs;
+    for (int item = 0; item < items; ++item) {
+        const int stage = item & 1, slab = item % slabs;
+        if (item + 1 < items) {
+            fetch_slab(item + 1, stage ^ 1);
             cp_async_commit();
             cp_async_wait<1>();
         } else {
@@ -500,16 +528,19 @@ __global__ void __launch_bounds__(HPT_THREADS) head_product_bf16_kernel(HeadProd
             }
         }
         __syncthreads();  // the next iteration's slab overwrites the other stage's reader
-    }
+        if (slab != slabs - 1) continue;
+        // the chunk is whole: out it goes, and the sums start again
+        const int n0 = (chunk0 + item / slabs) * HPT_OUTS;
 #pragma unroll
-    for (int r = 0; r < 2; ++r) {
-        const int t = warp * 16 + (lane >> 2) + r * 8;
-        if (t >= count) continue;
-        __nv_bfloat16* dst = a.out + (static_cast<size_t>(first + t) * a.heads + head) * out_head + n0;
+        for (int r = 0; r < 2; ++r) {
+            const int t = warp * 16 + (lane >> 2) + r * 8;
+            __nv_bfloat16* dst = a.out + (static_cast<size_t>(first + t) * a.heads + head) * out_head + n0;
 #pragma unroll
-        for (int n = 0; n < HPT_OUTS / 8; ++n) {
-            const int col = n * 8 + 2 * (lane & 3);
-            if (n0 + col < a.outs) *reinterpret_cast<uint32_t*>(dst + col) = pack_bf16(acc[n][r * 2], acc[n][r * 2 + 1]);
+            for (int n = 0; n < HPT_OUTS / 8; ++n) {
+                const int col = n * 8 + 2 * (lane & 3);
+                if (t < count && n0 + col < a.outs) *reinterpret_cast<uint32_t*>(dst + col) = pack_bf16(acc[n][r * 2], acc[n][r * 2 + 1]);
+                acc[n][r * 2] = acc[n][r * 2 + 1] = 0.0f;
+            }
         }
     }
     if (blockIdx.z != 0 || a.tail == 0) return;
@@ -548,8 +579,12 @@ ME_EXPORT int me_head_product_bf16(const void* in, int in_type, int splits, long
     if (smem > 200 * 1024) return ME_ERR_UNSUPPORTED;
     HeadProductParams a{in, splits, static_cast<size_t>(split_stride), static_cast<const __nv_bfloat16*>(weight),
                         reinterpret_cast<const float2*>(cos_sin), static_cast<__nv_bfloat16*>(out),
-                        tokens, heads, inner, outs, tail, rotary_dim};
-    const dim3 grid((tokens + HPT_TOKENS - 1) / HPT_TOKENS, heads, (outs + HPT_OUTS - 1) / HPT_OUTS);
+                        tokens, heads, inner, outs, tail, rotary_dim, 1};
+    // Many token tiles: one CTA walks all output chunks of its (tile, head), so x is fetched and rounded once.
+    // Few: a CTA per chunk, for the parallelism.
+    const int out_chunks = (outs + HPT_OUTS - 1) / HPT_OUTS;
+    if (static_cast<long long>((tokens + HPT_TOKENS - 1) / HPT_TOKENS) * heads >= 2 * 148) a.chunks_per_cta = out_chunks;
+    const dim3 grid((tokens + HPT_TOKENS - 1) / HPT_TOKENS, heads, (out_chunks + a.chunks_per_cta - 1) / a.chunks_per_cta);
     if (in_type == ME_F32) {
         auto kernel = head_product_bf16_kernel<true>;
         const int code = g_head_product_opt_in[0](kernel, 200 * 1024);  // once per device: the most any size needs
