@@ -35,6 +35,7 @@ LIBRARIES = {
     "attention_biased": "attention_biased.cu",
     "latent_attention": "latent_attention.cu",
     "latent_attention_bf16": "latent_attention_bf16.cu",
+    "latent_attention_tcgen05": "latent_attention_tcgen05.cu",
     "linear_attention": "linear_attention.cu",
     "recurrent": "recurrent.cu",
     "routing": "routing.cu",

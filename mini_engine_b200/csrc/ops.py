@@ -105,6 +105,13 @@ def raise_on_device_error() -> None:
     """Ask the tensor-core and attention libraries that are loaded whether a kernel gave up a
     bounded wait since the last call, and raise if one did: what such a kernel wrote is invalid.
     Reads a flag from the device, so it waits for the work in flight."""
+    latent_tc = 0
+    if "latent_attention_tcgen05" in build._loaded:
+        held = c_int(0)
+        status = _fn("latent_attention_tcgen05", "me_latent_attention_tcgen05_take_error", [ctypes.POINTER(c_int)])(ctypes.byref(held))
+        if status != 0:
+            raise KernelError(f"could not read the latent attention kernel's error flag (CUDA error {status})")
+        latent_tc = held.value
     latent = 0
     if "latent_attention_bf16" in build._loaded:
         held = c_int(0)
@@ -113,7 +120,7 @@ def raise_on_device_error() -> None:
             raise KernelError(f"could not read the latent attention kernel's error flag (CUDA error {status})")
         latent = held.value
     for what, code in (("tensor-core product", tensor_core.take_error()), ("attention", attention_bf16.take_error()),
-                       ("latent attention", latent)):  # fmt: skip
+                       ("latent attention", latent), ("latent attention (tcgen05)", latent_tc)):  # fmt: skip
         if code:
             raise KernelError(
                 f"a {what} kernel ran into the limit of a wait (code {code}): the results since the last check are invalid"
@@ -539,13 +546,44 @@ def latent_attention_supports(width: int, rank: int | None, kv_heads: int = 1) -
     return kv_heads == 1 and rank in (128, 256, 384, 512) and width % 64 == 0 and rank <= width and (160 * width + 2048) * 2 + 1024 <= 226 * 1024
 
 
+LATENT_TENSOR_MEMORY = True  # tests set it to False to run the mma.sync kernel where the tcgen05 one would be taken
+LATENT_TENSOR_MEMORY_MIN_ROWS = 64  # (token, head) pairs of the longest portion from which the tcgen05 kernel is taken
+_latent_query_maps: dict[tuple[int, int, int], Any] = {}
+
+
+def latent_tensor_memory_takes(width: int, rank: int, page_size: int, rows: int) -> bool:
+    """Whether prompt portions whose longest has ``rows`` (token, head) pairs take the tcgen05 kernel: the query rows
+    and one key tile must fit in shared memory, the output's halves must be whole 64-column blocks, pages whole
+    parts of a 64-key tile."""
+    return (LATENT_TENSOR_MEMORY and width % 64 == 0 and width <= 576 and rank in (128, 256, 384, 512) and rank <= width
+            and page_size in (8, 16, 32, 64) and rows >= LATENT_TENSOR_MEMORY_MIN_ROWS)  # fmt: skip
+
+
+def _latent_attention_tcgen05(q, pages, block_table, ctx, out, heads, width, rank, scale, window, gate, entries, ids, longest) -> None:
+    key = (q.data_ptr(), q.shape[0], q.shape[1])
+    q_map = _latent_query_maps.get(key)
+    if q_map is None:
+        if len(_latent_query_maps) > 8192:
+            _latent_query_maps.clear()
+        q_map = _latent_query_maps[key] = tensor_core._make_map(q.view(q.shape[0] * heads, width), 128)
+    fn = _fn("latent_attention_tcgen05", "me_latent_attention_tcgen05",
+             [c_void_p] * 8 + [c_float] + [c_int] * 8 + [c_void_p])  # fmt: skip
+    code = fn(
+        q_map, attention_bf16._page_map(pages), _ptr(block_table), _ptr(ctx.cu_tokens), _ptr(ctx.context_lens), _ptr(out),
+        _ptr(gate), _ptr(ids), scale, entries, longest, heads, width, rank, pages.shape[2], block_table.shape[1], window,
+        _stream(),
+    )  # fmt: skip
+    _check(code, "latent_attention_tcgen05")
+
+
 def latent_attention_bf16(q, pages, block_table, ctx, out, heads: int, width: int, rank: int, scale: float, window: int,
                           gate: torch.Tensor | None = None) -> None:  # fmt: skip
     """Attention of the batch's new tokens over a cache of one latent row per token (``pages [pages, 1, page_size,
     width]``) that is key and, in its first ``rank`` elements, value for every head; ``q [T, heads * width]``, ``out [T,
     heads * rank]``, ``gate`` float32 ``[T, heads]``.  Entries that bring one token split their keys over several CTAs
-    (spans of ``LATENT_SPAN`` keys by absolute position), the others take one CTA per 32 (token, head) pairs; a step
-    that holds both kinds is two launches, each over its own list of entries."""
+    (spans of ``LATENT_SPAN`` keys by absolute position); the others take the tcgen05 kernel (two CTAs per 128 (token,
+    head) pairs) when :func:`latent_tensor_memory_takes` says so, else one CTA per 32 pairs of the ``mma.sync`` kernel; a
+    step that holds both kinds is two launches, each over its own list of entries."""
     for name, t in (("q", q), ("out", out), ("pages", pages)):
         if t.dtype != torch.bfloat16 or not t.is_contiguous():
             raise KernelError(f"{name} must be contiguous bfloat16")
@@ -568,6 +606,9 @@ def latent_attention_bf16(q, pages, block_table, ctx, out, heads: int, width: in
     else:
         launches = [(False, ctx.num_entries, None, ctx.max_query_len)]
     for split, entries, ids, longest in launches:
+        if not split and latent_tensor_memory_takes(width, rank, pages.shape[2], longest * heads):
+            _latent_attention_tcgen05(q, pages, block_table, ctx, out, heads, width, rank, scale, window, gate, entries, ids, longest)
+            continue
         partials = counters = None
         max_splits = 1
         if split:

@@ -600,17 +600,21 @@ def test_tensor_memory_attention_with_a_window_and_the_options(heads, kv_heads, 
 
 @pytest.mark.parametrize("rank,rot", [(128, 64), (256, 64), (512, 64), (384, 0)])
 @pytest.mark.parametrize("heads,page", [(5, 4), (16, 16), (40, 16)])
-@pytest.mark.parametrize("news", [[1, 1, 1, 1], [90, 5, 130, 2], [1, 40, 1, 7]])
+@pytest.mark.parametrize("news", [[1, 1, 1, 1], [90, 5, 130, 2], [1, 40, 1, 7], [700, 64, 129, 300]])
 @pytest.mark.parametrize("window", [0, 70, 300])
-def test_tensor_core_attention_over_latent_rows(rank, rot, heads, page, news, window):
+@pytest.mark.parametrize("tensor_memory", [True, False])
+def test_tensor_core_attention_over_latent_rows(rank, rot, heads, page, news, window, tensor_memory, monkeypatch):
     """The bfloat16 kernel whose score rows are (token, head) pairs over one cached row per token that is key and,
     in its first elements, value: prompt portions, requests of one token whose keys are split over several CTAs (the
     longest context spans three of them), and both in one step, with a gate per head, over shuffled pages whose free
-    places hold large numbers, against float64.  One key of every request stands out for the first head."""
+    places hold large numbers, against float64.  One key of every request stands out for the first head.  Portions of
+    64 (token, head) pairs and more over pages of 8 to 64 tokens take the tcgen05 kernel (``tensor_memory``), or the
+    ``mma.sync`` kernel when it is switched off."""
     from test_kernels_gpu import fake_context
 
     from mini_engine_b200.csrc import ops
 
+    monkeypatch.setattr(ops, "LATENT_TENSOR_MEMORY", tensor_memory)
     width = rank + rot
     g = torch.Generator().manual_seed(rank + heads + page + len(news) + window + news[1])
     lengths = [700, 90, 130, 300]
@@ -692,10 +696,11 @@ def test_a_key_that_stands_out_at_the_windows_edge_on_tensor_cores(window, offse
 
 
 @pytest.mark.parametrize("heads,inner,outs,tail,dims", [(3, 128, 200, 16, 8), (2, 512, 128, 0, 0), (5, 64, 520, 64, 64), (1, 192, 8, 8, 0)])
-@pytest.mark.parametrize("tokens", [1, 70, 130])
+@pytest.mark.parametrize("tokens", [1, 70, 130, 3900])
 def test_products_per_head_on_tensor_cores(heads, inner, outs, tail, dims, tokens):
     """The bfloat16 products per head whose inner size is a multiple of 64 run on tensor cores: from partial sums and
-    from rounded rows, with a rotated tail, at token counts around the tile of 64."""
+    from rounded rows, with a rotated tail, at token counts around the tile of 64, and at one where a CTA walks all
+    output chunks of its tile (five heads of 3,900 tokens)."""
     from mini_engine_b200.csrc import ops
 
     torch.manual_seed(heads + inner + tokens)
