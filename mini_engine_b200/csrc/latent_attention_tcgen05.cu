@@ -17,7 +17,8 @@
 //             scores' own columns, row sums in float32; at the end O / sum * gate -> out
 //
 // Query rows take 128 x width x 2 bytes of shared memory and a key tile 64 x width x 2, so for widths up to 576 one
-// key tile fits beside the queries: the next tile is fetched when the second product has read this one.  Every wait
+// key tile fits beside the queries: of the next tile, the columns that this CTA's second product does not read are
+// fetched as soon as the scores are done, the others when the second product has read this tile.  Every wait
 // is bounded (tcgen05.cuh); a wait that ran out sets an error code, and the CTA frees its tensor memory and returns.
 #include "tcgen05.cuh"
 
@@ -48,6 +49,12 @@ __device__ __forceinline__ float lt_exp2(float x) {
     return y;
 }
 
+__device__ __forceinline__ float lt_max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+
 __device__ __forceinline__ uint32_t lt_pack(float lo, float hi) {
     uint32_t packed;
     asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(packed) : "f"(hi), "f"(lo));
@@ -64,19 +71,25 @@ latent_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const
     uint8_t* q_tile = tiles;                       // [blocks][128 rows][64]
     uint8_t* k_tile = tiles + blocks * LT_Q_BLOCK;  // [blocks][64 keys][64]
     uint64_t* bars = reinterpret_cast<uint64_t*>(k_tile + blocks * LT_K_BLOCK);
-    uint64_t *q_full = bars, *k_full = bars + 1, *k_empty = bars + 2, *s_full = bars + 3, *p_full = bars + 4,
-             *o_full = bars + 5;  // o_full: two, by the tile's parity
-    uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 7);
+    // The key tile has two parts with barriers of their own: the 64-column blocks that this CTA's second product
+    // reads as values ("c": free when that product is done) and the others ("rest": free when the scores are done, so
+    // that the next tile's share of them arrives while this tile's softmax and second product run).
+    uint64_t *q_full = bars, *c_full = bars + 1, *c_empty = bars + 2, *s_full = bars + 3, *p_full = bars + 4,
+             *o_full = bars + 5, *rest_full = bars + 7, *rest_empty = bars + 8;  // o_full: two, by the tile's parity
+    uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 9);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int half = blockIdx.x;
     const int row_block = gridDim.y - 1 - blockIdx.y;  // later blocks see more keys: they start first
     const int half_columns = p.rank / 2;
+    const int c_blocks = half_columns / 64, c_first = half * c_blocks;  // the blocks [c_first, c_first + c_blocks) are values here
 
     if (threadIdx.x == 0) {
         mbar_init(q_full, 1);
-        mbar_init(k_full, 1);
-        mbar_init(k_empty, 1);
+        mbar_init(c_full, 1);
+        mbar_init(c_empty, 1);
+        mbar_init(rest_full, 1);
+        mbar_init(rest_empty, 1);
         mbar_init(s_full, 1);
         mbar_init(p_full, LT_ROWS);
         mbar_init(o_full, 1);
@@ -125,15 +138,20 @@ latent_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const
                 // behind the window may have been given back, and what a row must not see is masked anyway.
                 const int index = min(max((first_tile + j) * pages_per_tile + lane, first_page_index), last_page_index);
                 const int page = loads ? table[index] : 0;
-                if (lane == 0) {
-                    ok = mbar_wait(k_empty, (j & 1) ^ 1);
-                    if (ok) mbar_expect_tx(k_full, blocks * LT_K_BLOCK);
-                    else atomicCAS(&g_latent_tc_error, 0, 1 << 8);
+                for (int part = 0; part < 2 && ok; ++part) {  // the rest first: it comes free first
+                    uint64_t* empty = part ? c_empty : rest_empty;
+                    uint64_t* full = part ? c_full : rest_full;
+                    if (lane == 0) {
+                        ok = mbar_wait(empty, (j & 1) ^ 1);
+                        if (ok) mbar_expect_tx(full, (part ? c_blocks : blocks - c_blocks) * LT_K_BLOCK);
+                        else atomicCAS(&g_latent_tc_error, 0, (1 << 8) | part);
+                    }
+                    ok = __shfl_sync(0xffffffffu, ok, 0);
+                    if (ok && loads)
+                        for (int b = 0; b < blocks; ++b)
+                            if ((b >= c_first && b < c_first + c_blocks) == (part == 1))
+                                tma_load_2d(k_tile + b * LT_K_BLOCK + lane * page_bytes, &map_k, b * 64, page * p.page_size, full);
                 }
-                ok = __shfl_sync(0xffffffffu, ok, 0);
-                if (ok && loads)
-                    for (int b = 0; b < blocks; ++b)
-                        tma_load_2d(k_tile + b * LT_K_BLOCK + lane * page_bytes, &map_k, b * 64, page * p.page_size, k_full);
             }
         }
     } else if (warp == 1) {
@@ -141,12 +159,12 @@ latent_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const
         if (lane == 0 && has_work) {
             constexpr uint32_t idesc_s = make_idesc(LT_KEYS);  // S[128 x 64] = Q K^T, K-major operands
             const uint32_t idesc_o = make_idesc(half_columns, true);  // O[128 x R/2] += P C, C is MN-major
-            const uint32_t c_tile = smem_u32(k_tile) + half * (half_columns / 64) * LT_K_BLOCK;  // this CTA's columns
+            const uint32_t c_tile = smem_u32(k_tile) + c_first * LT_K_BLOCK;  // this CTA's columns
             bool ok = mbar_wait(q_full, 0);
             if (!ok) atomicCAS(&g_latent_tc_error, 0, 2 << 8);
             for (int j = 0; j < tiles_count && ok; ++j) {
                 const uint32_t parity = j & 1;
-                ok = mbar_wait(k_full, parity);
+                ok = mbar_wait(rest_full, parity) && mbar_wait(c_full, parity);
                 if (!ok) { atomicCAS(&g_latent_tc_error, 0, (2 << 8) | 1); break; }
                 tcgen05_fence_after();
                 // The S columns are free once the previous second product has read P out of them: the MMAs of a
@@ -157,6 +175,7 @@ latent_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const
                                      smem_desc_sw128(smem_u32(k_tile) + k_offset), idesc_s, kk > 0 ? 1u : 0u);
                 }
                 tcgen05_commit(s_full);
+                tcgen05_commit(rest_empty);
                 ok = mbar_wait(p_full, parity);
                 if (!ok) { atomicCAS(&g_latent_tc_error, 0, (2 << 8) | 2); break; }
                 tcgen05_fence_after();
@@ -167,7 +186,7 @@ latent_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const
                     tcgen05_mma_bf16_ts(tmem_o, tmem_s + kk * 8, c_desc, idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
                 }
                 tcgen05_commit(o_full + (j & 1));
-                tcgen05_commit(k_empty);
+                tcgen05_commit(c_empty);
             }
         }
     } else if (has_work) {
@@ -194,15 +213,20 @@ latent_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const
             tcgen05_wait_ld();
             tcgen05_pin32(raw);
             tcgen05_pin32(raw + 32);
+            // raw stays unscaled (the scale is positive, so the maximum may be taken first); masked scores are -inf
             float best[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+            if (masked_tile) {
 #pragma unroll
-            for (int i = 0; i < 64; ++i) {
-                float x = __uint_as_float(raw[i]) * p.scale_log2;
-                if (masked_tile && (first_key + i > row_pos || first_key + i < lowest_seen)) x = -INFINITY;
-                raw[i] = __float_as_uint(x);
-                best[i & 3] = fmaxf(best[i & 3], x);
+                for (int i = 0; i < 64; ++i) {
+                    if (first_key + i > row_pos || first_key + i < lowest_seen) raw[i] = __float_as_uint(-INFINITY);
+                    best[i & 3] = fmaxf(best[i & 3], __uint_as_float(raw[i]));
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < 64; i += 2)  // two scores per instruction
+                    best[(i >> 1) & 3] = lt_max3(best[(i >> 1) & 3], __uint_as_float(raw[i]), __uint_as_float(raw[i + 1]));
             }
-            const float tile_max = fmaxf(fmaxf(best[0], best[1]), fmaxf(best[2], best[3]));
+            const float tile_max = fmaxf(fmaxf(best[0], best[1]), fmaxf(best[2], best[3])) * p.scale_log2;
             // The row's reference value follows its true maximum lazily: O is rescaled (and the second product of
             // the tile before waited for) only when the maximum of some row of the warp has grown by more than 2^8;
             // until then probabilities are taken relative to the older reference and may exceed 1.
@@ -228,20 +252,22 @@ latent_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const
                 }
             }
             const float base = row_max == -INFINITY ? 0.0f : row_max;
-            float partial[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            // exp2(score * scale - base) for two scores at a time with the two-wide float32 instructions
+            const float2 scale2 = make_float2(p.scale_log2, p.scale_log2), base2 = make_float2(-base, -base);
+            float2 partial[2] = {make_float2(0.0f, 0.0f), make_float2(0.0f, 0.0f)};
 #pragma unroll
             for (int c = 0; c < 2; ++c) {
                 uint32_t packed[16];
 #pragma unroll
                 for (int i = 0; i < 32; i += 2) {
-                    const float p0 = lt_exp2(__uint_as_float(raw[c * 32 + i]) - base);  // 2^-inf = 0
-                    const float p1 = lt_exp2(__uint_as_float(raw[c * 32 + i + 1]) - base);
-                    partial[(i >> 1) & 3] += p0 + p1;
-                    packed[i / 2] = lt_pack(p0, p1);
+                    const float2 x = __ffma2_rn(make_float2(__uint_as_float(raw[c * 32 + i]), __uint_as_float(raw[c * 32 + i + 1])), scale2, base2);
+                    const float2 pr = make_float2(lt_exp2(x.x), lt_exp2(x.y));  // 2^-inf = 0
+                    partial[(i >> 1) & 1] = __fadd2_rn(partial[(i >> 1) & 1], pr);
+                    packed[i / 2] = lt_pack(pr.x, pr.y);
                 }
                 tcgen05_st16(tmem_s + lane_base + c * 16, packed);  // P columns [16 c, +16) hold keys [32 c, +32)
             }
-            row_sum += (partial[0] + partial[1]) + (partial[2] + partial[3]);
+            row_sum += (partial[0].x + partial[0].y) + (partial[1].x + partial[1].y);
             tcgen05_wait_st();
             tcgen05_fence_before();
             mbar_arrive(p_full);
