@@ -2,6 +2,7 @@
 
     python -m mini_engine_b200.cli.design_bench [--design pimezen|molotar|bevadra] [--sizes 1b,8b] [--steps K] [--warmup W]
     (or: bench.py --design pimezen|molotar|bevadra)
+    python -m mini_engine_b200.cli.design_bench --design bevadra --sizes 8b --capture prompt|decode   (a few eager steps, for a profiler)
 
 For each size both models get the same width, feed-forward width, head counts, head size, layer count
 and vocabulary, seeded random bfloat16 weights, and the same two workloads: one prompt of 2,048 tokens
@@ -375,13 +376,50 @@ def run(sizes: list[str], steps: int, warmup: int, design: str = "pimezen") -> d
     return out
 
 
+def capture_steps(design: str, size_name: str, phase: str) -> None:
+    """A few eager steps of one model and nothing else, for a profiler: ``prompt`` is one 2,048-token step,
+    ``decode`` fills 8 contexts of 2,048 tokens and runs three steps of one token each."""
+    import torch
+
+    from mini_engine_b200 import EngineConfig, LLMEngine
+    from mini_engine_b200.csrc import ops
+    from mini_engine_b200.engine.runner import StepEntry
+
+    size = SIZES[size_name]
+    cfg = configs(size, design if design != "qwen3" else "pimezen")[design]
+    requests = 1 if phase == "prompt" else BATCH
+    pages = -(-(CONTEXT + 16) // BLOCK)
+    engine = LLMEngine.from_random(cfg, seed=0, config=EngineConfig(
+        block_size=BLOCK, num_blocks=requests * pages + 8, max_num_seqs=BATCH, max_num_batched_tokens=PROMPT,
+        max_model_len=4096, enable_prefix_caching=False, dtype=torch.bfloat16, cuda_graphs=False))  # fmt: skip
+    runner, manager = engine.runner, engine.block_manager
+    generator = torch.Generator().manual_seed(1)
+    caches = []
+    for _ in range(requests):
+        cache = manager.new_request()
+        assert manager.try_allocate(cache, CONTEXT + 16)
+        runner.execute([StepEntry(cache, 0, torch.randint(0, size["vocab"], (CONTEXT,), generator=generator).tolist(), (CONTEXT - 1,))])
+        caches.append(cache)
+    if phase == "decode":
+        for step in range(3):
+            runner.execute([StepEntry(cache, CONTEXT + step, [7], (0,)) for cache in caches])
+    torch.cuda.synchronize()
+    ops.raise_on_device_error()
+
+
 def main(argv=None) -> int:
     parser = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
     parser.add_argument("--design", choices=["pimezen", "molotar", "bevadra"], default="pimezen")
     parser.add_argument("--sizes", default="1b,8b")
     parser.add_argument("--steps", type=int, default=32)
     parser.add_argument("--warmup", type=int, default=5)
+    parser.add_argument("--capture", choices=["prompt", "decode"], default=None,
+                        help="run only a few eager steps of --model at the first of --sizes (for a profiler) and print nothing")
+    parser.add_argument("--model", default=None, help="with --capture: the design itself (default) or qwen3")
     args = parser.parse_args(argv)
+    if args.capture:
+        capture_steps(args.model or args.design, args.sizes.split(",")[0], args.capture)
+        return 0
     print(json.dumps(run(args.sizes.split(","), args.steps, max(args.warmup, 3), args.design)))
     return 0
 

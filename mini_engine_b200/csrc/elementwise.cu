@@ -475,8 +475,8 @@ static int launch_add_layernorm_vec(const LayerNormArgs& a, int count, cudaStrea
 template <typename OutT>
 static int launch_add_layernorm_lanes(const LayerNormArgs& a, int count, cudaStream_t stream) {
     const bool many = count >= NORM_MANY_ROWS;
-    if (a.hidden > 2048)
-        return many ? launch_add_layernorm_vec<OutT, 1024, 256>(a, count, stream) : launch_add_layernorm_vec<OutT, 1024, 1024>(a, count, stream);
+    if (a.hidden > 2048)  // (a block of 1,024 threads has 64 registers a thread, fewer than a lane's loads in flight need)
+        return many ? launch_add_layernorm_vec<OutT, 1024, 256>(a, count, stream) : launch_add_layernorm_vec<OutT, 1024, 512>(a, count, stream);
     if (a.hidden > 1024)
         return many ? launch_add_layernorm_vec<OutT, 512, 256>(a, count, stream) : launch_add_layernorm_vec<OutT, 512, 512>(a, count, stream);
     return launch_add_layernorm_vec<OutT, 256, 256>(a, count, stream);

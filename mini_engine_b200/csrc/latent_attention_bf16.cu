@@ -15,7 +15,7 @@
 // Scores, maxima, sums and the output accumulate in float32.  Keys outside the visible range are zero-filled in
 // shared memory and never read from the cache.  Requests that bring one token split their keys over several CTAs
 // (spans of 128 keys by absolute position, so the split depends on the position only); each writes a partial
-// (maximum, sum, unnormalised output) and the CTA that arrives last merges them in ascending key order.
+// (maximum, sum, unnormalised output) and a second launch of one CTA per (token, head) merges them in ascending key order.
 //
 // head_product_bf16: out[t][h][n] = sum_k x[t][h][k] W[h][k][n] on the same instructions: a CTA takes 64 tokens of
 // one head and 128 outputs, x rounded to bfloat16 once (it may arrive as float32 partial sums), W streamed in slabs of
@@ -38,7 +38,6 @@ struct LatentParams {
     __nv_bfloat16* out;          // [tokens][heads][R]
     const float* gate;           // [tokens][heads] multiplier of each head's output, or null
     float* partials;             // split: [entries][heads][max_splits][R + 2]
-    int* counters;               // split: [entries][row blocks] arrival counts, all zero between launches
     const int* entry_ids;        // the batch entries this launch covers (grid.z of them), or null: all, in order
     float scale_log2;            // scale * log2(e)
     int heads, width, page_size, table_width, window, max_splits;
@@ -263,7 +262,6 @@ __global__ void __launch_bounds__(LAT_THREADS, 1) latent_attention_kernel(Latent
 
     // A split request: this CTA's partial (unnormalised output, maximum, sum) of every row it holds.
     constexpr int STRIDE = R + 2;
-    const int active = last_slot - first_slot + 1;
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
         const int row = half * 16 + (lane >> 2) + r * 8;
@@ -274,88 +272,64 @@ __global__ void __launch_bounds__(LAT_THREADS, 1) latent_attention_kernel(Latent
             *reinterpret_cast<float2*>(dst + quarter * (R / 4) + n * 8 + 2 * (lane & 3)) = make_float2(acc[n][r * 2], acc[n][r * 2 + 1]);
         if (quarter == 0 && (lane & 3) == 0) dst[R] = row_max[r], dst[R + 1] = row_sum[r];
     }
-    // The CTA that finishes last among those of this (request, row block) merges their partials, always in
-    // ascending order of the keys, so the result does not depend on who is last.
-    __shared__ int is_last;
-    __threadfence();
+}
+
+// The partials of a split request -> out: grid (heads, entries), one (token, head) row per CTA.  The weight of a
+// partial is exp2(its maximum - the maximum of all), zero for one that saw no key; weighted sums and outputs are added
+// in ascending order of the keys, so the result depends on the positions alone.
+template <int R>
+__global__ void __launch_bounds__(128) latent_merge_kernel(LatentParams p) {
+    extern __shared__ float merge_smem[];  // weights [max_splits], weight * sum [max_splits]
+    __shared__ float warp_max[4];
+    __shared__ float total_shared;
+    constexpr int STRIDE = R + 2;
+    const int head = blockIdx.x;
+    pdl_trigger();
+    pdl_wait();
+    const int entry = p.entry_ids ? p.entry_ids[blockIdx.y] : blockIdx.y;
+    const int pos = p.context_lens[entry] - 1;  // the entry's one new token
+    const int lowest = p.window > 0 ? max(pos - p.window + 1, 0) : 0;
+    const int active = min(pos / LAT_SPAN - lowest / LAT_SPAN + 1, p.max_splits);
+    const size_t pair_index = static_cast<size_t>(p.cu_tokens[entry]) * p.heads + head;
+    const float* part = p.partials + (static_cast<size_t>(entry) * p.heads + head) * p.max_splits * STRIDE;
+    float* weights = merge_smem;
+    float* weighted = merge_smem + p.max_splits;
+    float total_max = -INFINITY;
+    for (int sl = threadIdx.x; sl < active; sl += 128) total_max = fmaxf(total_max, part[sl * STRIDE + R]);
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) total_max = fmaxf(total_max, __shfl_xor_sync(0xffffffffu, total_max, d));
+    if ((threadIdx.x & 31) == 0) warp_max[threadIdx.x >> 5] = total_max;
+    __syncthreads();
+    total_max = fmaxf(fmaxf(warp_max[0], warp_max[1]), fmaxf(warp_max[2], warp_max[3]));
+    for (int sl = threadIdx.x; sl < active; sl += 128) {
+        const float m = part[sl * STRIDE + R];
+        const float weight = m == -INFINITY ? 0.0f : exp2f(m - total_max);
+        weights[sl] = weight;
+        weighted[sl] = part[sl * STRIDE + R + 1] * weight;
+    }
     __syncthreads();
     if (threadIdx.x == 0) {
-        int* counter = p.counters + entry * gridDim.x + row_block;
-        const int ticket = atomicAdd(counter, 1);
-        is_last = ticket == active - 1;
-        if (is_last) *counter = 0;  // ready for the next launch
+        float total = 0.0f;
+        for (int sl = 0; sl < active; ++sl) total += weighted[sl];
+        total_shared = total;
     }
     __syncthreads();
-    if (!is_last) return;
-    __threadfence();
-    // Each row's weights first (a warp per row: exp2(maximum of the partial - maximum of all), zero for a partial that
-    // saw no key, and the weighted sums added in ascending order by one lane), into the shared memory that held the
-    // tiles; then every output element is one pass over the partials with nothing to wait for but its own loads.
-    const int capacity = (LAT_ROWS + 2 * LAT_KEYS) * p.width / 2;  // floats of the query and key tiles
-    if (LAT_ROWS * (2 * active + 1) <= capacity) {
-        float* weights = reinterpret_cast<float*>(smem);    // [32][active]
-        float* weighted = weights + LAT_ROWS * active;      // [32][active] weight * sum of the partial
-        float* totals = weighted + LAT_ROWS * active;       // [32]
-        for (int row = warp; row < rows_valid; row += LAT_THREADS / 32) {
-            const float* part = p.partials + (static_cast<size_t>(entry) * p.heads + row0 + row) * p.max_splits * STRIDE;
-            float total_max = -INFINITY;
-            for (int sl = lane; sl < active; sl += 32) total_max = fmaxf(total_max, __ldcg(part + sl * STRIDE + R));
+    const float whole = (p.gate ? p.gate[pair_index] : 1.0f) / total_shared;
+    for (int col = threadIdx.x * 2; col < R; col += 256) {
+        float2 value = make_float2(0.0f, 0.0f);
+        int sl = 0;
+        for (; sl + 4 <= active; sl += 4) {
+            float2 v[4];
 #pragma unroll
-            for (int d = 16; d > 0; d >>= 1) total_max = fmaxf(total_max, __shfl_xor_sync(0xffffffffu, total_max, d));
-            for (int sl = lane; sl < active; sl += 32) {
-                const float m = __ldcg(part + sl * STRIDE + R);
-                const float weight = m == -INFINITY ? 0.0f : exp2f(m - total_max);
-                weights[row * active + sl] = weight;
-                weighted[row * active + sl] = __ldcg(part + sl * STRIDE + R + 1) * weight;
-            }
-            __syncwarp();
-            if (lane == 0) {
-                float total = 0.0f;
-                for (int sl = 0; sl < active; ++sl) total += weighted[row * active + sl];
-                totals[row] = total;
-            }
-        }
-        __syncthreads();
-        for (int idx = threadIdx.x; idx < rows_valid * (R / 2); idx += LAT_THREADS) {
-            const int row = idx / (R / 2), col = (idx - row * (R / 2)) * 2;
-            const size_t pair_index = static_cast<size_t>(token0) * p.heads + row0 + row;
-            const float* part = p.partials + (static_cast<size_t>(entry) * p.heads + row0 + row) * p.max_splits * STRIDE + col;
-            const float* weight = weights + row * active;
-            float2 value = make_float2(0.0f, 0.0f);
-            int sl = 0;
-            for (; sl + 4 <= active; sl += 4) {
-                float2 v[4];
+            for (int j = 0; j < 4; ++j) v[j] = *reinterpret_cast<const float2*>(part + (sl + j) * STRIDE + col);
 #pragma unroll
-                for (int j = 0; j < 4; ++j) v[j] = __ldcg(reinterpret_cast<const float2*>(part + (sl + j) * STRIDE));
-#pragma unroll
-                for (int j = 0; j < 4; ++j) value.x = fmaf(v[j].x, weight[sl + j], value.x), value.y = fmaf(v[j].y, weight[sl + j], value.y);
-            }
-            for (; sl < active; ++sl) {
-                const float2 v = __ldcg(reinterpret_cast<const float2*>(part + sl * STRIDE));
-                value.x = fmaf(v.x, weight[sl], value.x), value.y = fmaf(v.y, weight[sl], value.y);
-            }
-            const float whole = (p.gate ? p.gate[pair_index] : 1.0f) / totals[row];
-            *reinterpret_cast<uint32_t*>(p.out + pair_index * R + col) = pack_bf16(value.x * whole, value.y * whole);
+            for (int j = 0; j < 4; ++j) value.x = fmaf(v[j].x, weights[sl + j], value.x), value.y = fmaf(v[j].y, weights[sl + j], value.y);
         }
-        return;
-    }
-    // more partials than the shared memory holds weights for: every element finds its weights itself
-    for (int idx = threadIdx.x; idx < rows_valid * R; idx += LAT_THREADS) {
-        const int row = idx / R, col = idx - row * R;
-        const size_t pair_index = static_cast<size_t>(token0) * p.heads + row0 + row;
-        const float* part = p.partials + (static_cast<size_t>(entry) * p.heads + row0 + row) * p.max_splits * STRIDE;
-        float total_max = -INFINITY;
-        for (int sl = 0; sl < active; ++sl) total_max = fmaxf(total_max, __ldcg(part + sl * STRIDE + R));
-        float value = 0.0f, total = 0.0f;
-        for (int sl = 0; sl < active; ++sl) {
-            const float m = __ldcg(part + sl * STRIDE + R);
-            if (m == -INFINITY) continue;
-            const float weight = exp2f(m - total_max);
-            value = fmaf(__ldcg(part + sl * STRIDE + col), weight, value);
-            total = fmaf(__ldcg(part + sl * STRIDE + R + 1), weight, total);
+        for (; sl < active; ++sl) {
+            const float2 v = *reinterpret_cast<const float2*>(part + sl * STRIDE + col);
+            value.x = fmaf(v.x, weights[sl], value.x), value.y = fmaf(v.y, weights[sl], value.y);
         }
-        const float gate = p.gate ? p.gate[pair_index] : 1.0f;
-        p.out[pair_index * R + col] = __float2bfloat16_rn(value / total * gate);
+        *reinterpret_cast<uint32_t*>(p.out + pair_index * R + col) = pack_bf16(value.x * whole, value.y * whole);
     }
 }
 
@@ -372,13 +346,18 @@ static SharedMemoryOptIn g_latent_opt_in[8];
 template <int R, bool SPLIT>
 static int launch_latent(const LatentParams& p, dim3 grid, size_t smem, cudaStream_t stream, int slot) {
     auto kernel = latent_attention_kernel<R, SPLIT>;
-    const int code = g_latent_opt_in[slot](kernel, LAT_MAX_SMEM);  // once per device: the most any width needs
+    int code = g_latent_opt_in[slot](kernel, LAT_MAX_SMEM);  // once per device: the most any width needs
     if (code != 0) return code;
-    return launch_kernel(kernel, grid, LAT_THREADS, smem, stream, p);
+    code = launch_kernel(kernel, grid, LAT_THREADS, smem, stream, p);
+    if (code != 0 || !SPLIT) return code;
+    const size_t merge_smem = 2 * static_cast<size_t>(p.max_splits) * sizeof(float);
+    if (merge_smem > 40 * 1024) return ME_ERR_UNSUPPORTED;
+    return launch_kernel(latent_merge_kernel<R>, dim3(p.heads, grid.z), 128, merge_smem, stream, p);
 }
 
 // `longest`: the most new tokens that an entry of the launch brings; `split` != 0: every entry brings one token,
-// `max_splits` CTAs share the keys of a (request, row block) and `partials` / `counters` are given.
+// `max_splits` CTAs share the keys of a (request, row block), `partials` is given, and a second launch merges them
+// (`counters` is not used).
 ME_EXPORT int me_latent_attention_bf16(const void* q, const void* pages, const int* block_table, const int* cu_tokens,
                                        const int* context_lens, void* out, const float* gate, float* partials,
                                        int* counters, const int* entry_ids, float scale, int entries, int longest,
@@ -386,9 +365,9 @@ ME_EXPORT int me_latent_attention_bf16(const void* q, const void* pages, const i
                                        int split, int max_splits, cudaStream_t stream) {
     if (entries <= 0 || longest <= 0) return 0;
     if (width % 64 || width < 64 || rank > width || heads < 1) return ME_ERR_UNSUPPORTED;
-    if (split && (partials == nullptr || counters == nullptr || max_splits < 1 || longest != 1)) return ME_ERR_ARGUMENT;
+    if (split && (partials == nullptr || max_splits < 1 || longest != 1)) return ME_ERR_ARGUMENT;
     LatentParams p{static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(pages), block_table, cu_tokens,
-                   context_lens, static_cast<__nv_bfloat16*>(out), gate, partials, counters, entry_ids,
+                   context_lens, static_cast<__nv_bfloat16*>(out), gate, partials, entry_ids,
                    scale * LAT_LOG2E, heads, width, page_size, table_width, window, max_splits};
     const size_t smem = (static_cast<size_t>(LAT_ROWS + 2 * LAT_KEYS) * width + LAT_ROWS * LAT_KEYS) * sizeof(__nv_bfloat16) +
                         8 * LAT_ROWS * sizeof(float);

@@ -615,7 +615,6 @@ def latent_attention_bf16(q, pages, block_table, ctx, out, heads: int, width: in
             keys = min(window, ctx.max_context_len) if window > 0 else ctx.max_context_len
             max_splits = (keys - 1) // LATENT_SPAN + 2 if window > 0 else -(-keys // LATENT_SPAN)
             partials = ctx.workspace.growing("latent.partials", (ctx.num_entries, heads, max_splits, rank + 2), torch.float32)
-            counters = ctx.workspace.zeroed("latent.counters", ctx.num_entries * (-(-heads // LATENT_ROWS)))
         code = fn(
             _ptr(q), _ptr(pages), _ptr(block_table), _ptr(ctx.cu_tokens), _ptr(ctx.context_lens), _ptr(out), _ptr(gate),
             _ptr(partials), _ptr(counters), _ptr(ids), scale, entries, longest, heads, width, rank, pages.shape[2],
