@@ -816,6 +816,31 @@ def test_one_latent_layer_and_one_biased_layer_against_plain(dtype_name, tmp_pat
         replay_and_compare(folder, dtype_name, schedules.changing_portions(requests), requests)
 
 
+# Sizes that the tensor-core kernels take: attention heads of 128 with a window (tcgen05 for portions of 32 tokens and
+# more, the split TMA kernel for single tokens), a reader of its keys with a wider window, latents of 128 and 256 with
+# 64 rotated elements (tcgen05 for portions of 64 (token, head) rows and more, split spans for single tokens).
+CONFIG_V = {
+    "architecture": "Bevadra", "vocab": 72, "width": 128, "norm": {"eps": 1e-5}, "logit_softcap": 20.0,
+    "layers": [
+        {"type": "attention", "mixer": attention(4, 2, 128, 128, 0.09, 70), "mlp": dense(128)},
+        {"type": "latent_attention", "mixer": latent(4, 32, 64, 32, 128, 64, 0.1, 50, 10000.0), "mlp": dense(64)},
+        {"type": "attention", "mixer": attention(4, 2, 128, 128, 0.08, 150, kv_from=0), "mlp": None},
+        {"type": "latent_attention", "mixer": latent(5, 64, 64, 48, 256, 128, 0.09, 200, 500.0, dims=32), "mlp": dense(128)},
+    ],
+}  # fmt: skip
+
+
+@pytest.mark.parametrize("schedule", ["whole", "tail_one_by_one", "changing_portions", "mixed"])
+def test_sizes_that_the_tensor_core_kernels_take(schedule, tmp_path_factory):
+    """A model whose bfloat16 steps run the tcgen05 and split kernels of both mixers, against the plain model, with
+    prompts longer than every window and than two blocks of 128 rows."""
+    folder = write_model(tmp_path_factory.mktemp("bevadra_V"), CONFIG_V, scale=6.0)
+    requests = {f"r{i}": random_ids(700 + i, n, CONFIG_V["vocab"]) for i, n in enumerate([300, 64, 161, 230, 33])}
+    maker = {"whole": schedules.whole, "changing_portions": schedules.changing_portions, "mixed": schedules.mixed,
+             "tail_one_by_one": lambda r: schedules.tail_one_by_one(r, 40)}[schedule]  # fmt: skip
+    replay_and_compare(folder, "bfloat16", maker(requests), requests)
+
+
 # ---------------------------------------------------------------------- the engine's own entry point
 
 
