@@ -1,6 +1,7 @@
 """Typed configuration: the model's own ``config.json`` keys and the engine's options."""
 
 from mini_engine_b200.config.bevadra import BevadraConfig
+from mini_engine_b200.config.bizurax import BizuraxConfig
 from mini_engine_b200.config.engine_config import EngineConfig
 from mini_engine_b200.config.model_spec import LayerSpec, ModelSpec, OrderEntry, PartSpec
 from mini_engine_b200.config.molotar import MolotarConfig
@@ -17,6 +18,7 @@ from mini_engine_b200.config.registry import (
 __all__ = [
     "Architecture",
     "BevadraConfig",
+    "BizuraxConfig",
     "EngineConfig",
     "LayerSpec",
     "ModelSpec",

@@ -10,7 +10,7 @@
 // (1 + sum exp(s))), or of a learned score per head (`sink_values`: exp(sink_h) in place of the 1); a multiplier
 // on the output (`gate`, float32 [tokens][heads][gate_width] with gate_width 1, one per head, or value_dim, one per
 // element); a distance bias that is linear in the distance (`slopes`, one per head: s -= slope_h * (p - j), after
-// the scale); and values that are the first value_dim elements of the key rows (`value_stride`: elements between
+// the scale); a cap on the scaled scores (`softcap`: s becomes softcap * tanh(s / softcap)); and values that are the first value_dim elements of the key rows (`value_stride`: elements between
 // two value rows; pass the key pages as value pages and head_dim as the stride).
 //
 // Keys are visited in tiles of 32 whose boundaries are multiples of 32 in *absolute position*
@@ -34,6 +34,7 @@ struct AttnArgs {
     int gate_width, value_stride;
     const float* slopes;       // [heads] or null
     const float* sink_values;  // [heads] or null (with sink: the silent participant's score, zero when null)
+    float softcap;             // > 0: the scaled score s becomes softcap * tanh(s / softcap)
 };
 
 constexpr int ATTN_WARPS = 4;
@@ -84,6 +85,7 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32) paged_attention_generic_kerne
             float dot = 0.0f;
             for (int i = 0; i < d; ++i) dot = fmaf(q[i], to_float(k_row[i]), dot);
             score = dot * a.scale;
+            if (a.softcap > 0.0f) score = a.softcap * tanhf(score / a.softcap);
             if (a.slopes) score -= slope * static_cast<float>(position - key);
         }
         const float new_max = fmaxf(running_max, warp_max(score));
@@ -128,7 +130,7 @@ ME_EXPORT int me_paged_attention_generic(const void* q, const void* k_pages, con
                                          int heads, int kv_heads, int head_dim, int page_size, int table_width,
                                          int window, int value_dim, int sink, const float* gate, int gate_width,
                                          int value_stride, const float* slopes, const float* sink_values,
-                                         cudaStream_t stream) {
+                                         float softcap, cudaStream_t stream) {
     if (tokens <= 0) return 0;
     if (gate && gate_width != 1 && gate_width != value_dim) return ME_ERR_ARGUMENT;
     if (value_stride < value_dim) return ME_ERR_ARGUMENT;
@@ -136,7 +138,7 @@ ME_EXPORT int me_paged_attention_generic(const void* q, const void* k_pages, con
         return ME_ERR_UNSUPPORTED;
     AttnArgs a{q, k_pages, v_pages, block_table, entry_of_token, positions, out, scale,
                tokens, heads, kv_heads, head_dim, page_size, table_width, window, value_dim, sink, gate,
-               gate_width, value_stride, slopes, sink_values};
+               gate_width, value_stride, slopes, sink_values, softcap};
     const long long items = static_cast<long long>(tokens) * heads;
     const int blocks = static_cast<int>((items + ATTN_WARPS - 1) / ATTN_WARPS);
     const size_t smem = static_cast<size_t>(ATTN_WARPS) * head_dim * sizeof(float);

@@ -37,6 +37,7 @@ LIBRARIES = {
     "latent_attention_bf16": "latent_attention_bf16.cu",
     "latent_attention_tcgen05": "latent_attention_tcgen05.cu",
     "linear_attention": "linear_attention.cu",
+    "hyper_connections": "hyper_connections.cu",
     "recurrent": "recurrent.cu",
     "routing": "routing.cu",
     "gemm_tcgen05": "gemm_tcgen05.cu",

@@ -1228,3 +1228,164 @@ ME_EXPORT int me_qk_wide_norm_rope_store(const float* qkv, int splits, long long
     if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     return launch_kernel(kernel, tokens, 256, smem, stream, a);
 }
+
+// ------------------------------------------------------ an activation on a product's partial sums
+
+// out[t][i] = act(sum_s partial[s][t][i]) in the compute dtype, for a feed-forward without a gate.
+// 0: relu(z)^2, 1: z * sigmoid(z), 2: the tanh form of GELU, 3: relu(z).
+enum : int { ACT_RELU_SQUARED = 0, ACT_SILU = 1, ACT_GELU_TANH = 2, ACT_RELU = 3 };
+
+__device__ __forceinline__ float plain_activation(float z, int activation) {
+    if (activation == ACT_RELU_SQUARED) { const float r = fmaxf(z, 0.0f); return r * r; }
+    if (activation == ACT_SILU) return z / (1.0f + expf(-z));
+    if (activation == ACT_GELU_TANH) return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+    return fmaxf(z, 0.0f);
+}
+
+template <typename OutT, int V>  // V consecutive elements per thread: 4 (16-byte loads) or 1
+__global__ void activation_kernel(const float* __restrict__ partial, int splits, size_t split_stride,
+                                  OutT* __restrict__ out, size_t total, int activation) {
+    pdl_trigger();
+    pdl_wait();
+    for (size_t idx = (blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x) * V; idx < total;
+         idx += static_cast<size_t>(gridDim.x) * blockDim.x * V) {
+        if constexpr (V == 4) {
+            float4 z = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            for (int s = 0; s < splits; ++s) add4(z, *reinterpret_cast<const float4*>(partial + s * split_stride + idx));
+            store4(out + idx, make_float4(plain_activation(z.x, activation), plain_activation(z.y, activation),
+                                          plain_activation(z.z, activation), plain_activation(z.w, activation)));
+        } else {
+            float z = 0.0f;
+            for (int s = 0; s < splits; ++s) z += partial[s * split_stride + idx];
+            out[idx] = from_float<OutT>(plain_activation(z, activation));
+        }
+    }
+}
+
+ME_EXPORT int me_activation(const float* partial, int splits, long long split_stride, void* out, int out_type,
+                            int tokens, int width, int activation, cudaStream_t stream) {
+    if (tokens <= 0) return 0;
+    if (activation < ACT_RELU_SQUARED || activation > ACT_RELU) return ME_ERR_ARGUMENT;
+    const size_t total = static_cast<size_t>(tokens) * width;
+    const bool vec = width % 4 == 0 && split_stride % 4 == 0 && aligned16(partial) && aligned16(out);
+    const int threads = 256;
+    const int blocks = static_cast<int>(std::min<size_t>((total / (vec ? 4 : 1) + threads - 1) / threads, 148 * 32));
+    const size_t stride = static_cast<size_t>(split_stride);
+    if (out_type == ME_BF16) {
+        auto* o = static_cast<__nv_bfloat16*>(out);
+        return vec ? launch_kernel(activation_kernel<__nv_bfloat16, 4>, blocks, threads, 0, stream, partial, splits, stride, o, total, activation)
+                   : launch_kernel(activation_kernel<__nv_bfloat16, 1>, blocks, threads, 0, stream, partial, splits, stride, o, total, activation);
+    }
+    auto* o = static_cast<float*>(out);
+    return vec ? launch_kernel(activation_kernel<float, 4>, blocks, threads, 0, stream, partial, splits, stride, o, total, activation)
+               : launch_kernel(activation_kernel<float, 1>, blocks, threads, 0, stream, partial, splits, stride, o, total, activation);
+}
+
+// --------------------------------------- bias + rotary + unit norm behind the rotation + cache write
+
+// One warp per (token, head) over the columns of qkv = [q heads | k heads | v heads]: the partial sums and the
+// bias are added, the first rotary_dim elements of a q or k head are rotated (element e pairs with e +
+// rotary_dim / 2), and then, with `unit_norm`, the rotated head is divided by its root mean square over head_dim
+// (eps inside the root, no weight).  q goes to q_out, k and v to the token's cache slot (or to dense buffers).
+// Lane l holds elements l, l + 32, ... and adds their squares in ascending order; the lanes meet in a butterfly.
+struct UnitQkvArgs {
+    const float* qkv;  // [splits][tokens][row_width]
+    int splits;
+    size_t split_stride;
+    int row_width;
+    const float* bias;      // [row_width] or null
+    const float2* cos_sin;  // [tokens][rotary_dim / 2] or null
+    const int* slot_mapping;
+    void* q_out;
+    void* k_pages;
+    void* v_pages;
+    void* k_dense;
+    void* v_dense;
+    float eps;
+    int tokens, heads, kv_heads, head_dim, value_dim, page_size, rotary_dim, unit_norm;
+};
+
+constexpr int UNIT_WARPS = 4;
+constexpr int UNIT_MAX_PER_LANE = 16;  // head sizes up to 512
+
+template <typename OutT>
+__global__ void __launch_bounds__(UNIT_WARPS * 32) qkv_rope_unit_store_kernel(UnitQkvArgs a) {
+    extern __shared__ float staged[];  // [UNIT_WARPS][max(head_dim, value_dim)]
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int per_token = a.heads + 2 * a.kv_heads;
+    const long long item = static_cast<long long>(blockIdx.x) * UNIT_WARPS + warp;
+    pdl_trigger();
+    pdl_wait();
+    if (item >= static_cast<long long>(a.tokens) * per_token) return;
+    const int token = static_cast<int>(item / per_token), which = static_cast<int>(item % per_token);
+    const int q_width = a.heads * a.head_dim, k_width = a.kv_heads * a.head_dim;
+    const bool is_q = which < a.heads, is_k = !is_q && which < a.heads + a.kv_heads;
+    const int head = is_q ? which : is_k ? which - a.heads : which - a.heads - a.kv_heads;
+    const int d = (is_q || is_k) ? a.head_dim : a.value_dim;
+    const int column = is_q ? head * d : is_k ? q_width + head * d : q_width + k_width + head * d;
+    float* mine = staged + warp * max(a.head_dim, a.value_dim);
+    const float* src = a.qkv + static_cast<size_t>(token) * a.row_width + column;
+    for (int e = lane; e < d; e += 32) {
+        float v = 0.0f;
+        for (int s = 0; s < a.splits; ++s) v += src[s * a.split_stride + e];
+        if (a.bias) v += a.bias[column + e];
+        mine[e] = v;
+    }
+    __syncwarp();
+    float value[UNIT_MAX_PER_LANE];
+    float sum_sq = 0.0f;
+    const int half = a.rotary_dim / 2;
+    const float2* angles = (a.cos_sin && (is_q || is_k)) ? a.cos_sin + static_cast<size_t>(token) * half : nullptr;
+#pragma unroll
+    for (int j = 0; j < UNIT_MAX_PER_LANE; ++j) {
+        const int e = lane + 32 * j;
+        if (e >= d) break;
+        float v = mine[e];
+        if (angles && e < a.rotary_dim) {
+            const float other = mine[e < half ? e + half : e - half];
+            const float2 angle = angles[e < half ? e : e - half];
+            v = e < half ? v * angle.x - other * angle.y : v * angle.x + other * angle.y;
+        }
+        value[j] = v;
+        sum_sq = fmaf(v, v, sum_sq);
+    }
+    float inv = 1.0f;
+    if (a.unit_norm && (is_q || is_k)) inv = rsqrtf(warp_sum(sum_sq) / static_cast<float>(d) + a.eps);
+    OutT* dst;
+    if (is_q) {
+        dst = static_cast<OutT*>(a.q_out) + static_cast<size_t>(token) * q_width + column;
+    } else if (a.slot_mapping) {
+        const int slot = a.slot_mapping[token];
+        if (slot < 0) return;
+        const size_t page = slot / a.page_size, offset = slot % a.page_size;
+        dst = static_cast<OutT*>(is_k ? a.k_pages : a.v_pages) + ((page * a.kv_heads + head) * a.page_size + offset) * d;
+    } else {
+        dst = static_cast<OutT*>(is_k ? a.k_dense : a.v_dense) + static_cast<size_t>(token) * a.kv_heads * d + head * d;
+    }
+#pragma unroll
+    for (int j = 0; j < UNIT_MAX_PER_LANE; ++j) {
+        const int e = lane + 32 * j;
+        if (e >= d) break;
+        dst[e] = from_float<OutT>(value[j] * inv);
+    }
+}
+
+ME_EXPORT int me_qkv_rope_unit_store(const float* qkv, int splits, long long split_stride, int row_width,
+                                     const float* bias, const float* cos_sin, const int* slot_mapping, void* q_out,
+                                     void* k_pages, void* v_pages, void* k_dense, void* v_dense, float eps, int out_type,
+                                     int tokens, int heads, int kv_heads, int head_dim, int value_dim, int page_size,
+                                     int rotary_dim, int unit_norm, cudaStream_t stream) {
+    if (tokens <= 0) return 0;
+    if (rotary_dim < 0 || rotary_dim > head_dim || rotary_dim % 2) return ME_ERR_ARGUMENT;
+    if (row_width < (heads + kv_heads) * head_dim + kv_heads * value_dim) return ME_ERR_ARGUMENT;
+    if (head_dim < 1 || value_dim < 1 || head_dim > 32 * UNIT_MAX_PER_LANE || value_dim > 32 * UNIT_MAX_PER_LANE)
+        return ME_ERR_UNSUPPORTED;
+    UnitQkvArgs a{qkv, splits, (size_t)split_stride, row_width, bias, reinterpret_cast<const float2*>(cos_sin), slot_mapping,
+                  q_out, k_pages, v_pages, k_dense, v_dense, eps, tokens, heads, kv_heads, head_dim, value_dim, page_size,
+                  rotary_dim, unit_norm};
+    const long long items = static_cast<long long>(tokens) * (heads + 2 * kv_heads);
+    const int blocks = static_cast<int>((items + UNIT_WARPS - 1) / UNIT_WARPS);
+    const size_t smem = static_cast<size_t>(UNIT_WARPS) * std::max(head_dim, value_dim) * sizeof(float);
+    if (out_type == ME_BF16) return launch_kernel(qkv_rope_unit_store_kernel<__nv_bfloat16>, blocks, UNIT_WARPS * 32, smem, stream, a);
+    return launch_kernel(qkv_rope_unit_store_kernel<float>, blocks, UNIT_WARPS * 32, smem, stream, a);
+}

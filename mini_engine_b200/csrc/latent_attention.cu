@@ -20,7 +20,7 @@
 // ------------------------------------------------------------------- down projection's finish
 
 struct DownArgs {
-    const float* down;  // [splits][tokens][row_width]: q latent (q_rank) | c (kv_rank) | k_rot (rot_dim) | gates
+    const float* down;  // [splits][tokens][row_width]: q latent (q_rank, may be 0) | c (kv_rank) | k_rot (rot_dim) | gates
     int splits;
     size_t split_stride;
     int row_width;
@@ -68,7 +68,7 @@ __global__ void __launch_bounds__(256) latent_down_finish_kernel(DownArgs a) {
     float q_total = 0.0f, c_total = 0.0f;
 #pragma unroll
     for (int w = 0; w < 8; ++w) q_total += warp_partial[0][w], c_total += warp_partial[1][w];
-    const float q_inv = rsqrtf(q_total / static_cast<float>(a.q_rank) + a.eps);
+    const float q_inv = a.q_rank > 0 ? rsqrtf(q_total / static_cast<float>(a.q_rank) + a.eps) : 1.0f;  // no query latent: nothing to norm
     const float c_inv = rsqrtf(c_total / static_cast<float>(a.kv_rank) + a.eps);
     const int half = a.rotary_dim / 2;
     const float2* angles = a.cos_sin ? a.cos_sin + static_cast<size_t>(token) * half : nullptr;
@@ -105,7 +105,7 @@ ME_EXPORT int me_latent_down_finish(const float* down, int splits, long long spl
                                     int gates, cudaStream_t stream) {
     if (tokens <= 0) return 0;
     if (rotary_dim < 0 || rotary_dim > rot_dim || rotary_dim % 2) return ME_ERR_ARGUMENT;
-    if (row_width < q_rank + kv_rank + rot_dim + gates || q_rank < 1 || kv_rank < 1) return ME_ERR_ARGUMENT;
+    if (row_width < q_rank + kv_rank + rot_dim + gates || q_rank < 0 || kv_rank < 1) return ME_ERR_ARGUMENT;
     if (gates > 0 && gate_out == nullptr) return ME_ERR_ARGUMENT;
     const size_t smem = static_cast<size_t>(row_width) * sizeof(float);
     if (smem > 200 * 1024) return ME_ERR_UNSUPPORTED;

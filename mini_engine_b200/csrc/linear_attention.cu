@@ -270,7 +270,87 @@ ME_EXPORT int me_gla_scan(const float* proj, int splits, long long split_stride,
     return ME_ERR_UNSUPPORTED;
 }
 
-// out[t][h][e] = weight[e] * o[t][h][e] * rsqrt(mean_e(o^2) + eps) * silu(gate[t][h][e]).
+// ------------------------------------------------------------------- retention: a fixed decay per head
+
+// Retention is the same recurrence with a constant decay per head in the place of the data-dependent one per
+// channel, rotated queries and keys, and keys scaled by k_scale:
+//
+//   S_t = a_h S_(t-1) + k_t v_t^T,  o_t = S_t^T q_t,  q_t = rot(W_q h_t),  k_t = rot(W_k h_t) * k_scale.
+//
+// Its prepare kernel fills the scan's input: the sums of the product's partial sums, the rotation of the first
+// rotary_dim elements of every head (element e pairs with e + rotary_dim / 2, angles from the step's table), the
+// key scale and the head's decay for every channel, float32.  The scan kernel above then walks the tokens.
+struct RetentionPrepArgs {
+    const float* proj;  // [splits][tokens][width]
+    int splits;
+    size_t split_stride;
+    int width;
+    int q_col, k_col;
+    const float2* cos_sin;  // [tokens][rotary_dim / 2] or null
+    const float* decay;     // [heads]
+    float* prepared;        // [tokens][heads][3][dim]
+    float k_scale;
+    int tokens, heads, dim, rotary_dim;
+};
+
+__global__ void __launch_bounds__(256) retention_prepare_kernel(RetentionPrepArgs a) {
+    const size_t total = static_cast<size_t>(a.tokens) * a.heads * a.dim;
+    const int half = a.rotary_dim / 2;
+    pdl_trigger();
+    pdl_wait();
+    for (size_t idx = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; idx < total;
+         idx += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        const int d = static_cast<int>(idx % a.dim);
+        const int head = static_cast<int>((idx / a.dim) % a.heads);
+        const size_t token = idx / (static_cast<size_t>(a.dim) * a.heads);
+        const float* row = a.proj + token * a.width + head * a.dim;
+        float q = 0.0f, k = 0.0f;
+        for (int p = 0; p < a.splits; ++p) {
+            q += row[p * a.split_stride + a.q_col + d];
+            k += row[p * a.split_stride + a.k_col + d];
+        }
+        if (a.cos_sin && d < a.rotary_dim) {
+            const int partner = d < half ? d + half : d - half;
+            float q_other = 0.0f, k_other = 0.0f;
+            for (int p = 0; p < a.splits; ++p) {
+                q_other += row[p * a.split_stride + a.q_col + partner];
+                k_other += row[p * a.split_stride + a.k_col + partner];
+            }
+            const float2 angle = a.cos_sin[token * half + (d < half ? d : d - half)];
+            q = d < half ? q * angle.x - q_other * angle.y : q * angle.x + q_other * angle.y;
+            k = d < half ? k * angle.x - k_other * angle.y : k * angle.x + k_other * angle.y;
+        }
+        float* dst = a.prepared + ((token * a.heads + head) * 3) * a.dim + d;
+        dst[0] = q;
+        dst[a.dim] = k * a.k_scale;
+        dst[2 * a.dim] = a.decay[head];
+    }
+}
+
+ME_EXPORT int me_retention_scan(const float* proj, int splits, long long split_stride, int width, int q_col, int k_col,
+                                int v_col, const float* cos_sin, int rotary_dim, const float* decay, float k_scale,
+                                const int* cu_tokens, const int* state_slots, const int* fresh, float* state, float* out,
+                                float* prepared, int tokens, int entries, int heads, int dim, int vdim,
+                                cudaStream_t stream) {
+    if (entries <= 0 || tokens <= 0) return 0;
+    if (dim < 1 || vdim < 1 || heads < 1 || rotary_dim < 0 || rotary_dim > dim || rotary_dim % 2) return ME_ERR_ARGUMENT;
+    RetentionPrepArgs p{proj, splits, static_cast<size_t>(split_stride), width, q_col, k_col,
+                        reinterpret_cast<const float2*>(cos_sin), decay, prepared, k_scale, tokens, heads, dim, rotary_dim};
+    const size_t total = static_cast<size_t>(tokens) * heads * dim;
+    const int blocks = static_cast<int>(std::min<size_t>((total + 255) / 256, 148 * 16));
+    const int code = launch_kernel(retention_prepare_kernel, blocks, 256, 0, stream, p);
+    if (code) return code;
+    ScanArgs a{proj, splits, static_cast<size_t>(split_stride), width, v_col, prepared, cu_tokens, state_slots,
+               fresh, state, out, heads, dim, vdim};
+    if (dim <= 16) return launch_scan<16>(a, entries, stream);
+    if (dim <= 32) return launch_scan<32>(a, entries, stream);
+    if (dim <= 64) return launch_scan<64>(a, entries, stream);
+    if (dim <= 128) return launch_scan<128>(a, entries, stream);
+    if (dim <= 192) return launch_scan<192>(a, entries, stream);
+    return ME_ERR_UNSUPPORTED;
+}
+
+// out[t][h][e] = weight[e] * o[t][h][e] * rsqrt(mean_e(o^2) + eps) * silu(gate[t][h][e]); a null weight is all ones.
 template <typename T>
 __global__ void __launch_bounds__(128) gla_finish_kernel(const float* __restrict__ o, const float* __restrict__ proj,
                                                          int splits, size_t split_stride, int width, int g_col,
@@ -294,7 +374,7 @@ __global__ void __launch_bounds__(128) gla_finish_kernel(const float* __restrict
         float gate = 0.0f;
         for (int p = 0; p < splits; ++p) gate += gate_row[p * split_stride + e];
         const float activated = gate / (1.0f + expf(-gate));
-        dst[e] = from_float<T>(weight[e] * (row[e] * inv) * activated);
+        dst[e] = from_float<T>((weight ? weight[e] : 1.0f) * (row[e] * inv) * activated);
     }
 }
 

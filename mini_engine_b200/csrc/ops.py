@@ -464,9 +464,10 @@ def gemm_tensor_core_swiglu(plan, x: torch.Tensor, act: torch.Tensor, activation
 def paged_attention_generic(
     q, k_pages, v_pages, block_table, entry_of_token, positions, out, heads, kv_heads, head_dim, scale, window,
     value_dim: int | None = None, sink: bool = False, gate: torch.Tensor | None = None,
-    slopes: torch.Tensor | None = None, sink_values: torch.Tensor | None = None,
+    slopes: torch.Tensor | None = None, sink_values: torch.Tensor | None = None, softcap: float = 0.0,
 ) -> None:
-    """One warp per (token, head), any head size; ``value_dim``: width of a value head when it differs;
+    """One warp per (token, head), any head size; ``softcap`` > 0: a scaled score ``s`` becomes ``softcap * tanh(s /
+    softcap)``; ``value_dim``: width of a value head when it differs;
     ``sink``: one more participant of score zero and no value in the softmax, or of the learned score
     ``sink_values[h]`` (float32 ``[heads]``); ``gate`` (float32 ``[T, heads]`` or ``[T, heads * value_dim]``): a
     multiplier on each head's output, or on each of its elements; ``slopes`` (float32 ``[heads]``): ``slopes[h] *
@@ -500,13 +501,13 @@ def paged_attention_generic(
     fn = _fn(
         "attention_generic",
         "me_paged_attention_generic",
-        [c_void_p] * 7 + [c_int, c_float] + [c_int] * 9 + [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p],
+        [c_void_p] * 7 + [c_int, c_float] + [c_int] * 9 + [c_void_p, c_int, c_int, c_void_p, c_void_p, c_float, c_void_p],
     )
     code = fn(
         _ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(block_table), _ptr(entry_of_token), _ptr(positions), _ptr(out),
         _type_code(q.dtype), scale, q.shape[0], heads, kv_heads, head_dim, k_pages.shape[2], block_table.shape[1],
         window, value_dim, 1 if (sink or sink_values is not None) else 0, _ptr(gate), gate_width, value_stride,
-        _ptr(slopes), _ptr(sink_values), _stream(),
+        _ptr(slopes), _ptr(sink_values), float(softcap or 0.0), _stream(),
     )  # fmt: skip
     _check(code, "paged_attention_generic")
 
@@ -514,18 +515,18 @@ def paged_attention_generic(
 def paged_attention(
     *, q, k_pages, v_pages, block_table, ctx, out, heads: int, kv_heads: int, head_dim: int, scale: float, window: int,
     value_dim: int | None = None, sink: bool = False, gate: torch.Tensor | None = None,
-    slopes: torch.Tensor | None = None, sink_values: torch.Tensor | None = None,
+    slopes: torch.Tensor | None = None, sink_values: torch.Tensor | None = None, softcap: float = 0.0,
 ) -> None:  # fmt: skip
     """Causal attention of the batch's new tokens over their requests' cached keys (the new
     tokens' own keys are already in the cache).  Chooses the kernel by dtype and sizes.  ``value_dim``,
     ``sink``, ``gate``, ``slopes`` and ``sink_values`` as in :func:`paged_attention_generic`; value heads of another
     width than the key heads and values inside the key rows (``v_pages=None``) take that kernel."""
     if v_pages is None and q.dtype == torch.bfloat16 and latent_attention_supports(head_dim, value_dim, kv_heads):
-        if sink or slopes is not None or sink_values is not None:
-            raise KernelError("attention over latent rows takes a window and a gate per head, no sink and no distance bias")
+        if sink or slopes is not None or sink_values is not None or softcap:
+            raise KernelError("attention over latent rows takes a window and a gate per head, no sink, no distance bias and no cap")
         latent_attention_bf16(q, k_pages, block_table, ctx, out, heads, head_dim, value_dim, scale, window, gate)
         return
-    if v_pages is not None and q.dtype == torch.bfloat16 and value_dim in (None, head_dim):
+    if v_pages is not None and q.dtype == torch.bfloat16 and value_dim in (None, head_dim) and not softcap:
         if attention_bf16.supports(head_dim, heads, kv_heads):
             attention_bf16.paged_attention(
                 q, k_pages, v_pages, block_table, ctx, out, heads, kv_heads, head_dim, scale, window, sink=sink, gate=gate,
@@ -534,7 +535,7 @@ def paged_attention(
             return
     paged_attention_generic(
         q, k_pages, v_pages, block_table, ctx.entry_of_token, ctx.positions, out, heads, kv_heads, head_dim,
-        scale, window, value_dim=value_dim, sink=sink, gate=gate, slopes=slopes, sink_values=sink_values,
+        scale, window, value_dim=value_dim, sink=sink, gate=gate, slopes=slopes, sink_values=sink_values, softcap=softcap,
     )  # fmt: skip
 
 
@@ -624,21 +625,25 @@ def latent_attention_bf16(q, pages, block_table, ctx, out, heads: int, width: in
 
 
 def latent_down_finish(
-    *, down: torch.Tensor, q_rank: int, kv_rank: int, rot_dim: int, q_weight: torch.Tensor, kv_weight: torch.Tensor,
-    eps: float, cos_sin: torch.Tensor | None, slot_mapping: torch.Tensor, q_latent: torch.Tensor, k_pages: torch.Tensor,
+    *, down: torch.Tensor, q_rank: int, kv_rank: int, rot_dim: int, q_weight: torch.Tensor | None, kv_weight: torch.Tensor,
+    eps: float, cos_sin: torch.Tensor | None, slot_mapping: torch.Tensor, q_latent: torch.Tensor | None, k_pages: torch.Tensor,
     gates: int = 0, gate_out: torch.Tensor | None = None,
 ) -> None:  # fmt: skip
     """The row ``[query latent | c | k_rot | gates]`` of a fused down projection (``down``: ``[S, T, width]`` float32
     partial sums): RMS norm of the query latent into ``q_latent [T, q_rank]`` and of ``c`` (each with its weight),
     rotation of the first ``rotary_dim`` elements of ``k_rot``, the write of ``[c | k_rot]`` to the token's slot of
-    ``k_pages [pages, 1, page_size, kv_rank + rot_dim]``, and ``sigmoid`` of the gates into ``gate_out [T, gates]``."""
-    _need(down, torch.float32, "down"), _need(q_latent, None, "q_latent"), _need(k_pages, q_latent.dtype, "k_pages")
-    _need(q_weight, torch.float32, "q_weight"), _need(kv_weight, torch.float32, "kv_weight")
+    ``k_pages [pages, 1, page_size, kv_rank + rot_dim]``, and ``sigmoid`` of the gates into ``gate_out [T, gates]``.
+    ``q_rank=0``: the row has no query latent (``q_weight`` and ``q_latent`` are ``None``)."""
+    _need(down, torch.float32, "down"), _need(k_pages, None, "k_pages"), _need(kv_weight, torch.float32, "kv_weight")
+    if q_rank:
+        _need(q_latent, k_pages.dtype, "q_latent"), _need(q_weight, torch.float32, "q_weight")
+    elif q_latent is not None or q_weight is not None:
+        raise KernelError("latent_down_finish: without a query latent there is neither its weight nor its output")
     _need(slot_mapping, torch.int32, "slot_mapping")
     splits, tokens, width = down.shape
     if width != q_rank + kv_rank + rot_dim + gates:
         raise KernelError(f"the down projection's width {width} is not q_rank + kv_rank + rot_dim + gates")
-    if q_weight.shape != (q_rank,) or kv_weight.shape != (kv_rank,) or q_latent.shape != (tokens, q_rank):
+    if kv_weight.shape != (kv_rank,) or (q_rank and (q_weight.shape != (q_rank,) or q_latent.shape != (tokens, q_rank))):
         raise KernelError("latent_down_finish: norm weights or q_latent do not fit the ranks")
     if k_pages.dim() != 4 or k_pages.shape[1] != 1 or k_pages.shape[3] != kv_rank + rot_dim:
         raise KernelError(f"key pages {tuple(k_pages.shape)} are not [pages, 1, page_size, kv_rank + rot_dim]")
@@ -656,7 +661,7 @@ def latent_down_finish(
              [c_void_p, c_int, c_longlong, c_int, c_void_p, c_void_p, c_float] + [c_void_p] * 5 + [c_int] * 7 + [c_void_p])  # fmt: skip
     code = fn(
         _ptr(down), splits, down.stride(0), width, _ptr(q_weight), _ptr(kv_weight), float(eps), _ptr(cos_sin),
-        _ptr(slot_mapping), _ptr(q_latent), _ptr(k_pages), _ptr(gate_out), _type_code(q_latent.dtype), tokens, q_rank,
+        _ptr(slot_mapping), _ptr(q_latent), _ptr(k_pages), _ptr(gate_out), _type_code(k_pages.dtype), tokens, q_rank,
         kv_rank, rot_dim, rotary_dim, gates, _stream(),
     )  # fmt: skip
     _check(code, "latent_down_finish")
@@ -841,11 +846,14 @@ def gla_scan(
 
 
 def gla_finish(
-    *, o: torch.Tensor, proj: torch.Tensor, gate_column: int, weight: torch.Tensor, eps: float, out: torch.Tensor,
+    *, o: torch.Tensor, proj: torch.Tensor, gate_column: int, weight: torch.Tensor | None, eps: float, out: torch.Tensor,
     heads: int, vdim: int,
 ) -> None:  # fmt: skip
-    """``out = weight * o / rms(o) * silu(gate)`` per (token, head); the gate is a column range of ``proj``."""
-    _need(o, torch.float32, "o"), _need(proj, torch.float32, "proj"), _need(weight, torch.float32, "weight"), _need(out, None, "out")
+    """``out = weight * o / rms(o) * silu(gate)`` per (token, head); the gate is a column range of ``proj``;
+    ``weight=None`` is a weight of ones."""
+    _need(o, torch.float32, "o"), _need(proj, torch.float32, "proj"), _need(out, None, "out")
+    if weight is not None:
+        _need(weight, torch.float32, "weight")
     tokens = o.shape[0]
     fn = _fn(
         "linear_attention",
@@ -857,6 +865,175 @@ def gla_finish(
         _type_code(out.dtype), tokens, heads, vdim, _stream(),
     )  # fmt: skip
     _check(code, "gla_finish")
+
+
+def retention_scan(
+    *, proj: torch.Tensor, columns: dict[str, int], cos_sin: torch.Tensor | None, decay: torch.Tensor, k_scale: float, ctx,
+    state: torch.Tensor, out: torch.Tensor, prepared: torch.Tensor, heads: int, dim: int, vdim: int,
+) -> None:  # fmt: skip
+    """The recurrence ``S_t = decay_h S_(t-1) + k_t v_t^T``, ``o_t = S_t^T q_t`` over the batch's tokens, entry by entry,
+    from and into each request's state slot.  ``proj`` is ``[S, T, width]`` float32 partial sums whose ``columns`` ``q, k,
+    v`` say where each projection starts; q and k are rotated by ``cos_sin [T, rotary_dim / 2, 2]`` (their first
+    ``rotary_dim`` elements per head, rotate-half) and k is multiplied by ``k_scale``; ``decay`` is float32 ``[heads]``;
+    ``out`` is float32 ``[T, heads, vdim]``; ``prepared`` is float32 scratch of ``T * heads * 3 * dim`` values."""
+    _need(proj, torch.float32, "proj"), _need(decay, torch.float32, "decay"), _need(state, torch.float32, "state")
+    _need(out, torch.float32, "out"), _need(prepared, torch.float32, "prepared")
+    tokens = proj.shape[1]
+    if decay.shape != (heads,) or state.shape[1:] != (heads, dim, vdim):
+        raise KernelError("retention_scan: decay or state do not fit heads/dim/vdim")
+    if prepared.numel() < tokens * heads * 3 * dim or out.numel() < tokens * heads * vdim:
+        raise KernelError("retention_scan: scratch or output too small")
+    rotary_dim = 0
+    if cos_sin is not None:
+        _need(cos_sin, torch.float32, "cos_sin")
+        rotary_dim = 2 * cos_sin.shape[1] if cos_sin.dim() == 3 else -1
+        if cos_sin.dim() != 3 or cos_sin.shape[0] != tokens or cos_sin.shape[2] != 2 or not 2 <= rotary_dim <= dim:
+            raise KernelError(f"cos_sin {tuple(cos_sin.shape)} is not [tokens, rotary_dim / 2, 2] with rotary_dim <= dim")
+    fn = _fn(
+        "linear_attention",
+        "me_retention_scan",
+        [c_void_p, c_int, c_longlong] + [c_int] * 4 + [c_void_p, c_int, c_void_p, c_float] + [c_void_p] * 6 + [c_int] * 5 + [c_void_p],
+    )
+    code = fn(
+        _ptr(proj), proj.shape[0], proj.stride(0), proj.shape[2], columns["q"], columns["k"], columns["v"], _ptr(cos_sin),
+        rotary_dim, _ptr(decay), float(k_scale), _ptr(ctx.cu_tokens), _ptr(ctx.state_slots), _ptr(ctx.fresh), _ptr(state),
+        _ptr(out), _ptr(prepared), tokens, ctx.num_entries, heads, dim, vdim, _stream(),
+    )  # fmt: skip
+    _check(code, "retention_scan")
+
+
+def _hyper_update(pending, mix, share, count):
+    if pending is None:
+        return 0, 0
+    _need(pending, torch.float32, "pending"), _need(mix, torch.float32, "mix"), _need(share, torch.float32, "share")
+    if mix.shape != (count, count) or share.shape != (count,):
+        raise KernelError("hyper-connections: the mixing matrix is [streams, streams] and there is one share per stream")
+    return pending.shape[0], pending.stride(0)
+
+
+def hyper_step(
+    *, streams: torch.Tensor, seed: torch.Tensor | None, pending: torch.Tensor | None, mix: torch.Tensor | None,
+    share: torch.Tensor | None, mult: float, read: torch.Tensor | None, weight: torch.Tensor, eps: float,
+    out: torch.Tensor, rows: torch.Tensor | None = None,
+) -> None:  # fmt: skip
+    """One sublayer boundary of a model with several residual streams ``streams [S, T, hidden]`` (float32).  First the
+    update that the previous sublayer's output ``pending [P, T, hidden]`` (partial sums) is owed: ``x_t = sum_s mix[s,
+    t] x_s + mult * share[t] * sum_p pending[p]``, written back; then ``out = weight * rmsnorm(sum_t read[t] x_t)``.
+    ``seed [T, hidden]``: the streams have not been written yet and all equal these rows.  ``pending=None``: no update,
+    nothing is written.  ``read=None``: the plain sum of the streams.  ``rows`` (int32): only these rows, nothing is
+    written back."""
+    _need(streams, torch.float32, "streams"), _need(weight, torch.float32, "weight"), _need(out, None, "out")
+    count, tokens, hidden = streams.shape
+    splits, stride = _hyper_update(pending, mix, share, count)
+    if pending is not None and pending.shape[1:] != (tokens, hidden):
+        raise KernelError(f"hyper_step: pending {tuple(pending.shape)} does not fit the streams {tuple(streams.shape)}")
+    if seed is not None:
+        _need(seed, torch.float32, "seed")
+        if seed.shape != (tokens, hidden):
+            raise KernelError("hyper_step: the seed rows must be [tokens, hidden]")
+    if read is not None:
+        _need(read, torch.float32, "read")
+        if read.shape != (count,):
+            raise KernelError("hyper_step: one read weight per stream")
+    if rows is not None:
+        _need(rows, torch.int32, "rows")
+    produced = tokens if rows is None else rows.shape[0]
+    if weight.shape != (hidden,) or out.shape != (produced, hidden):
+        raise KernelError("hyper_step: weight or out do not fit")
+    fn = _fn(
+        "hyper_connections",
+        "me_hyper_step",
+        [c_void_p, c_longlong, c_void_p, c_void_p, c_int, c_longlong, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_float,
+         c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p],
+    )  # fmt: skip
+    code = fn(
+        _ptr(streams), streams.stride(0), _ptr(seed), _ptr(pending), splits, stride, _ptr(mix), _ptr(share), float(mult),
+        _ptr(read), _ptr(weight), float(eps), _ptr(out), _type_code(out.dtype), _ptr(rows), produced, hidden, count, _stream(),
+    )  # fmt: skip
+    _check(code, "hyper_step")
+
+
+def hyper_sum(
+    *, streams: torch.Tensor, seed: torch.Tensor | None, pending: torch.Tensor | None, mix: torch.Tensor | None,
+    share: torch.Tensor | None, mult: float, out: torch.Tensor,
+) -> None:  # fmt: skip
+    """``out [T, hidden]`` (float32): the sum of the residual streams after the update that ``pending`` is owed (see
+    :func:`hyper_step`); nothing else is written."""
+    _need(streams, torch.float32, "streams"), _need(out, torch.float32, "out")
+    count, tokens, hidden = streams.shape
+    splits, stride = _hyper_update(pending, mix, share, count)
+    if out.shape != (tokens, hidden):
+        raise KernelError("hyper_sum: out must be [tokens, hidden]")
+    fn = _fn(
+        "hyper_connections",
+        "me_hyper_sum",
+        [c_void_p, c_longlong, c_void_p, c_void_p, c_int, c_longlong, c_void_p, c_void_p, c_float, c_void_p, c_int, c_int, c_int, c_void_p],
+    )
+    code = fn(
+        _ptr(streams), streams.stride(0), _ptr(seed), _ptr(pending), splits, stride, _ptr(mix), _ptr(share), float(mult),
+        _ptr(out), tokens, hidden, count, _stream(),
+    )  # fmt: skip
+    _check(code, "hyper_sum")
+
+
+PLAIN_ACTIVATIONS = {"relu_squared": 0, "silu": 1, "gelu_tanh": 2, "relu": 3}
+
+
+def activation(partials: torch.Tensor, out: torch.Tensor, kind: str) -> None:
+    """``out = act(sum_s partials[s])`` in the dtype of ``out``: ``relu_squared`` (``max(z, 0)^2``), ``silu``,
+    ``gelu_tanh`` or ``relu``, for a feed-forward without a gate."""
+    if kind not in PLAIN_ACTIVATIONS:
+        raise KernelError(f"activation: kind must be one of {sorted(PLAIN_ACTIVATIONS)}, got {kind!r}")
+    _need(partials, torch.float32, "partials"), _need(out, None, "out")
+    splits, tokens, width = partials.shape
+    if out.shape != (tokens, width):
+        raise KernelError(f"activation: out {tuple(out.shape)} does not fit partials {tuple(partials.shape)}")
+    fn = _fn("elementwise", "me_activation", [c_void_p, c_int, c_longlong, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
+    code = fn(_ptr(partials), splits, partials.stride(0), _ptr(out), _type_code(out.dtype), tokens, width,
+              PLAIN_ACTIVATIONS[kind], _stream())  # fmt: skip
+    _check(code, "activation")
+
+
+def qkv_rope_unit_store(
+    *, qkv: torch.Tensor, heads: int, kv_heads: int, head_dim: int, value_dim: int, bias: torch.Tensor | None,
+    cos_sin: torch.Tensor | None, unit_norm_eps: float | None, q_out: torch.Tensor, page_size: int,
+    slot_mapping: torch.Tensor | None = None, k_pages: torch.Tensor | None = None, v_pages: torch.Tensor | None = None,
+    k_dense: torch.Tensor | None = None, v_dense: torch.Tensor | None = None,
+) -> None:  # fmt: skip
+    """``qkv [S, T, width]`` float32 partial sums with the columns ``[q | k | v]``: add ``bias`` (float32 ``[width]``),
+    rotate the first ``rotary_dim`` elements of every q and k head by ``cos_sin [T, rotary_dim / 2, 2]``, then (with
+    ``unit_norm_eps``) divide every rotated q and k head by its root mean square over ``head_dim``, eps inside the root;
+    q goes to ``q_out``, k and v to their cache slots (or dense buffers)."""
+    _need(qkv, torch.float32, "qkv"), _need(q_out, None, "q_out")
+    splits, tokens, width = qkv.shape
+    if width != (heads + kv_heads) * head_dim + kv_heads * value_dim:
+        raise KernelError(f"qkv width {width} does not fit the head sizes")
+    if slot_mapping is None and (k_dense is None or v_dense is None):
+        raise KernelError("either slot_mapping with pages or dense outputs must be given")
+    if slot_mapping is not None:
+        _need(slot_mapping, torch.int32, "slot_mapping")
+        if k_pages is None or v_pages is None or k_pages.dtype != q_out.dtype or v_pages.dtype != q_out.dtype:
+            raise KernelError("pages must be given in the dtype of q_out")
+        if k_pages.shape[1:] != (kv_heads, page_size, head_dim) or v_pages.shape[1:] != (kv_heads, page_size, value_dim):
+            raise KernelError(f"pages {tuple(k_pages.shape)}, {tuple(v_pages.shape)} do not fit kv_heads/page_size/head_dim")
+    rotary_dim = 0
+    if cos_sin is not None:
+        _need(cos_sin, torch.float32, "cos_sin")
+        rotary_dim = 2 * cos_sin.shape[1] if cos_sin.dim() == 3 else -1
+        if cos_sin.dim() != 3 or cos_sin.shape[0] != tokens or cos_sin.shape[2] != 2 or not 2 <= rotary_dim <= head_dim:
+            raise KernelError(f"cos_sin {tuple(cos_sin.shape)} is not [tokens, rotary_dim / 2, 2] with rotary_dim <= head_dim")
+    if bias is not None:
+        _need(bias, torch.float32, "bias")
+        if bias.shape != (width,):
+            raise KernelError(f"bias {tuple(bias.shape)} does not fit the {width} columns of qkv")
+    fn = _fn("elementwise", "me_qkv_rope_unit_store",
+             [c_void_p, c_int, c_longlong, c_int] + [c_void_p] * 8 + [c_float] + [c_int] * 9 + [c_void_p])  # fmt: skip
+    code = fn(
+        _ptr(qkv), splits, qkv.stride(0), width, _ptr(bias), _ptr(cos_sin), _ptr(slot_mapping), _ptr(q_out), _ptr(k_pages),
+        _ptr(v_pages), _ptr(k_dense), _ptr(v_dense), float(unit_norm_eps or 0.0), _type_code(q_out.dtype), tokens, heads,
+        kv_heads, head_dim, value_dim, page_size, rotary_dim, 1 if unit_norm_eps is not None else 0, _stream(),
+    )  # fmt: skip
+    _check(code, "qkv_rope_unit_store")
 
 
 def pair_embedding(
@@ -992,23 +1169,35 @@ def rglru(
     _check(code, "rglru")
 
 
+ROUTE_SCORINGS = {"sigmoid": 0, "softmax_chosen": 1}
+
+
 def route(
     *, h: torch.Tensor, router: torch.Tensor, weights: torch.Tensor, chosen: torch.Tensor, chosen_weight: torch.Tensor,
-    top: int, group_count: int, group_keep: int, weight_scale: float,
+    top: int, group_count: int, group_keep: int, weight_scale: float, bias: torch.Tensor | None = None,
+    scoring: str = "sigmoid",
 ) -> None:  # fmt: skip
     """Per token the ``top`` units with the largest ``sigmoid(router h)`` among the units of the ``group_keep`` best
     of ``group_count`` equal groups of neighbours (a group's value: the sum of its two largest scores); weights are
     the chosen scores over their sum, times ``weight_scale``.  ``weights [T, units]`` float32 gets them densely (zero
-    elsewhere), ``chosen`` (int32) and ``chosen_weight`` (float32) ``[T, top]`` as lists."""
+    elsewhere), ``chosen`` (int32) and ``chosen_weight`` (float32) ``[T, top]`` as lists.  ``bias`` (float32 ``[units]``)
+    is added to ``router h``.  ``scoring="softmax_chosen"``: the units with the largest logits are chosen and their weights
+    are the softmax over the chosen logits only (times ``weight_scale``)."""
+    if scoring not in ROUTE_SCORINGS:
+        raise KernelError(f"route: scoring must be one of {sorted(ROUTE_SCORINGS)}, got {scoring!r}")
+    if bias is not None:
+        _need(bias, torch.float32, "bias")
+        if bias.shape != (router.shape[0],):
+            raise KernelError("route: one bias per unit")
     _need(h, None, "h"), _need(router, torch.float32, "router"), _need(weights, torch.float32, "weights")
     _need(chosen, torch.int32, "chosen"), _need(chosen_weight, torch.float32, "chosen_weight")
     tokens, hidden = h.shape
     units = router.shape[0]
     if router.shape != (units, hidden) or weights.shape != (tokens, units) or chosen.shape != (tokens, top) or chosen_weight.shape != (tokens, top):
         raise KernelError("route: shapes do not fit")
-    fn = _fn("routing", "me_route", [c_void_p, c_int] + [c_void_p] * 4 + [c_int] * 6 + [c_float, c_void_p])
+    fn = _fn("routing", "me_route", [c_void_p, c_int, c_void_p, c_void_p, c_int] + [c_void_p] * 3 + [c_int] * 6 + [c_float, c_void_p])
     code = fn(
-        _ptr(h), _type_code(h.dtype), _ptr(router), _ptr(weights), _ptr(chosen), _ptr(chosen_weight), tokens, hidden,
+        _ptr(h), _type_code(h.dtype), _ptr(router), _ptr(bias), ROUTE_SCORINGS[scoring], _ptr(weights), _ptr(chosen), _ptr(chosen_weight), tokens, hidden,
         units, int(top), int(group_count), int(group_keep), float(weight_scale), _stream(),
     )  # fmt: skip
     _check(code, "route")

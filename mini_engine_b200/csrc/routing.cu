@@ -1,6 +1,7 @@
 // The router of a feed-forward made of many small units ("experts") of which a token uses a few.
 //
-// Per token: z = W_r h in float32 (h in the compute dtype, W_r float32), s = sigmoid(z).  The units form
+// Per token: z = W_r h (+ a bias per unit) in float32 (h in the compute dtype, W_r float32), s = sigmoid(z); in
+// mode 1, s = z itself and the chosen units' weights are the softmax over the chosen logits only.  The units form
 // `group_count` equal groups of neighbours; a group's value is the sum of its two largest scores (of its
 // only score when a group is a single unit) and only units of the `group_keep` best groups are eligible.
 // Among those the `top` largest scores are chosen; their weights are s / (sum of the chosen s + 1e-20) *
@@ -17,6 +18,8 @@ constexpr int MAX_UNITS = 1024;
 struct RouteArgs {
     const void* h;        // [tokens][hidden]
     const float* router;  // [units][hidden]
+    const float* bias;    // [units] added to the logits, or null
+    int mode;             // 0: sigmoid scores over their sum; 1: the largest logits, softmax over the chosen ones
     float* weights;       // [tokens][units]
     int* chosen;          // [tokens][top]
     float* chosen_weight; // [tokens][top]
@@ -53,7 +56,8 @@ __global__ void __launch_bounds__(ROUTE_WARPS * 32) route_kernel(RouteArgs a) {
             for (int i = lane; i < a.hidden; i += 32) sum = fmaf(to_float(h[i]), w[i], sum);
         }
         sum = warp_sum(sum);
-        if (lane == 0) score[unit] = 1.0f / (1.0f + expf(-sum));
+        if (a.bias) sum += a.bias[unit];
+        if (lane == 0) score[unit] = a.mode == 1 ? sum : 1.0f / (1.0f + expf(-sum));
     }
     for (int unit = threadIdx.x; unit < a.units; unit += ROUTE_WARPS * 32) {
         eligible[unit] = 0;
@@ -93,24 +97,32 @@ __global__ void __launch_bounds__(ROUTE_WARPS * 32) route_kernel(RouteArgs a) {
         eligible[best] = 2;
         total += best_score;
     }
-    const float inv = a.weight_scale / (total + 1e-20f);
+    float inv = a.weight_scale / (total + 1e-20f), top_logit = 0.0f;
+    if (a.mode == 1) {  // exp(z - max) over the sum of the chosen: the first choice holds the largest logit
+        top_logit = chosen[0] >= 0 ? score[chosen[0]] : 0.0f;
+        float denom = 0.0f;
+        for (int turn = 0; turn < a.top; ++turn)
+            if (chosen[turn] >= 0) denom += expf(score[chosen[turn]] - top_logit);
+        inv = a.weight_scale / denom;
+    }
     for (int turn = 0; turn < a.top; ++turn) {
         const int u = chosen[turn];
-        const float weight = u >= 0 ? score[u] * inv : 0.0f;
+        const float weight = u < 0 ? 0.0f : a.mode == 1 ? expf(score[u] - top_logit) * inv : score[u] * inv;
         chosen_weight[turn] = weight;
         if (u >= 0) a.weights[static_cast<size_t>(token) * a.units + u] = weight;
     }
 }
 
-ME_EXPORT int me_route(const void* h, int h_type, const float* router, float* weights, int* chosen,
-                       float* chosen_weight, int tokens, int hidden, int units, int top, int group_count,
+ME_EXPORT int me_route(const void* h, int h_type, const float* router, const float* bias, int mode, float* weights,
+                       int* chosen, float* chosen_weight, int tokens, int hidden, int units, int top, int group_count,
                        int group_keep, float weight_scale, cudaStream_t stream) {
     if (tokens <= 0) return 0;
     if (units < 1 || units > MAX_UNITS) return ME_ERR_UNSUPPORTED;
     if (group_count < 1 || units % group_count || group_keep < 1 || group_keep > group_count || top < 1 ||
         top > group_keep * (units / group_count))
         return ME_ERR_ARGUMENT;
-    RouteArgs a{h, router, weights, chosen, chosen_weight, tokens, hidden, units, top, group_count, group_keep, weight_scale};
+    if (mode != 0 && mode != 1) return ME_ERR_ARGUMENT;
+    RouteArgs a{h, router, bias, mode, weights, chosen, chosen_weight, tokens, hidden, units, top, group_count, group_keep, weight_scale};
     if (h_type == ME_BF16) return launch_kernel(route_kernel<__nv_bfloat16>, tokens, ROUTE_WARPS * 32, 0, stream, a);
     return launch_kernel(route_kernel<float>, tokens, ROUTE_WARPS * 32, 0, stream, a);
 }

@@ -1,3 +1,3 @@
 """Architectures.  Importing this package registers the built-in ones."""
 
-from mini_engine_b200.models import bevadra, molotar, pimezen, qwen3  # noqa: F401
+from mini_engine_b200.models import bevadra, bizurax, molotar, pimezen, qwen3  # noqa: F401

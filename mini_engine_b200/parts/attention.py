@@ -36,6 +36,11 @@ number per head (tensor ``sink``), ``p_j = exp(s_j) / (exp(sink_h) + sum_i exp(s
 the concatenated heads element by element with ``sigmoid(W_g x)``, ``W_g [heads * value_dim, hidden]``, again as rows
 of the fused product; ``o_bias`` gives the output projection a bias, which the block hands to the norm that adds
 the projection's partial sums.  With these, ``qkv_bias`` may be combined.
+
+And two for designs that normalise behind the rotation and bound their scores: ``unit_norm_eps`` divides every q and
+k head, *after* its rotation, by its root mean square over ``head_dim`` (eps inside the root, no weight), in the
+kernel that adds the biases, rotates and writes the cache; ``score_softcap`` replaces a scaled score ``s`` by ``cap *
+tanh(s / cap)``.  They combine with ``qkv_bias``, ``value_dim``, ``scale``, a partial rotation and either sink.
 """
 
 from __future__ import annotations
@@ -87,6 +92,8 @@ class GroupedQueryAttention(Mixer):
         element_gate: bool = False,
         o_bias: bool = False,
         linear_bias_span: float = 8.0,
+        unit_norm_eps: float | None = None,
+        score_softcap: float | None = None,
     ):
         if num_heads % kv_heads:
             raise ValueError(f"num_heads ({num_heads}) must be a multiple of kv_heads ({kv_heads})")
@@ -107,23 +114,32 @@ class GroupedQueryAttention(Mixer):
         if self.head_gate and self.element_gate:
             raise ValueError("a mixer gates its heads or its elements, not both")
         self.has_output_bias = bool(o_bias)
+        self.unit_norm_eps = None if unit_norm_eps is None else float(unit_norm_eps)
+        self.softcap = float(score_softcap) if score_softcap else 0.0
+        if self.softcap < 0.0:
+            raise ValueError(f"score_softcap must be positive, got {score_softcap}")
+        # The kernel that adds biases, rotates, then divides by the root mean square: it stands where the other
+        # stores would, in front of the attention kernels that know a sink and a cap.
+        self.unit_store = self.unit_norm_eps is not None or bool(self.softcap)
+        if self.unit_store and (qk_norm_eps is not None or head_gate or element_gate or distance_bias or talking_heads or keep_first or reads_shared_cache or o_bias):
+            raise ValueError("unit_norm_eps and score_softcap do not combine with q/k norm weights, gates, distance biases, talking heads, keep_first, an output bias or a shared cache")
         # Whether q, k, v (and the gates) leave the fused product through the kernel that normalises whole projections.
         self.wide_store = self.wide_norm or self.head_gate or self.element_gate or self.linear_bias
         if (self.head_gate or self.element_gate or self.linear_bias) and qk_norm_eps is not None and not self.wide_norm:
             raise ValueError("gates and the linear distance bias come with qk_norm_scope='projection' or without q/k norms")
         if (self.wide_store or self.sink) and (keep_first or distance_bias or talking_heads):
             raise ValueError("qk_norm_scope='projection', softmax_sink, gates and the linear distance bias do not combine with keep_first, the logarithmic distance_bias or talking_heads")
-        if qkv_bias and self.sink and not self.wide_store:
+        if qkv_bias and self.sink and not self.wide_store and not self.unit_store:
             raise ValueError("biases with a sink need the projection-wide store (a gate, a linear bias or qk_norm_scope='projection')")
         self.extended = bool(
-            (self.value_dim != head_dim and not (self.wide_store or self.sink)) or self.keep_first or distance_bias or talking_heads
+            (self.value_dim != head_dim and not (self.wide_store or self.sink or self.unit_store)) or self.keep_first or distance_bias or talking_heads
         )
         if self.extended:
             if reads_shared_cache or qkv_bias:
                 raise ValueError("the extended attention options do not combine with a shared cache or biases")
             if head_dim < 1 or self.value_dim < 1 or keep_first < 0:
                 raise ValueError("head sizes must be positive and keep_first must not be negative")
-        elif self.wide_store or self.sink:  # these run in the kernel that takes any head size
+        elif self.wide_store or self.sink or self.unit_store:  # these run in the kernel that takes any head size
             if not (1 <= head_dim <= 512 and 1 <= self.value_dim <= 512):
                 raise ValueError(f"head sizes must lie between 1 and 512, got {head_dim} and {self.value_dim}")
         else:
@@ -250,6 +266,8 @@ class GroupedQueryAttention(Mixer):
         q = ctx.buffer("attn.q", (tokens, self.heads * d), ctx.dtype)
         table = self.position.step_angles(ctx) if self.position is not None else None
         slots = ctx.slot_mapping[cache.group]
+        if self.unit_store:
+            return self._forward_unit(qkv, q, table, slots, ctx, cache)
         if self.wide_store or self.sink:
             return self._forward_gated(qkv, q, table, slots, ctx, cache)
         args: dict[str, Any] = dict(
@@ -307,6 +325,24 @@ class GroupedQueryAttention(Mixer):
             q=q, k_pages=cache.k, v_pages=cache.v, block_table=ctx.block_tables[cache.group], ctx=ctx,
             out=out, heads=self.heads, kv_heads=self.kv_heads, head_dim=d, scale=self.scale,
             window=self.window or 0,
+        )  # fmt: skip
+        return self.out.forward(out, ctx, "attn.o")
+
+    def _forward_unit(self, qkv, q, table, slots, ctx: StepContext, cache: LayerCache) -> torch.Tensor:
+        """The step with q and k normalised behind their rotation and (or) capped scores."""
+        tokens = q.shape[0]
+        if self.position is not None and table is None:
+            raise ValueError("these attention options take a rotation that the fused kernel applies, or none")
+        ops.qkv_rope_unit_store(
+            qkv=qkv, heads=self.heads, kv_heads=self.kv_heads, head_dim=self.head_dim, value_dim=self.value_dim,
+            bias=self.bias, cos_sin=table, unit_norm_eps=self.unit_norm_eps, q_out=q, page_size=ctx.page_size,
+            slot_mapping=slots, k_pages=cache.k, v_pages=cache.v,
+        )  # fmt: skip
+        out = ctx.buffer("attn.out", (tokens, self.heads * self.value_dim), ctx.dtype)
+        ops.paged_attention(
+            q=q, k_pages=cache.k, v_pages=cache.v, block_table=ctx.block_tables[cache.group], ctx=ctx, out=out,
+            heads=self.heads, kv_heads=self.kv_heads, head_dim=self.head_dim, scale=self.scale, window=self.window or 0,
+            value_dim=self.value_dim, sink=self.sink, sink_values=self.sink_values, softcap=self.softcap,
         )  # fmt: skip
         return self.out.forward(out, ctx, "attn.o")
 

@@ -79,6 +79,13 @@ class Residual:
     bias of the output projection whose partial sums are pending, added with them.  ``pending_more`` is
     the output of a second sublayer that read the same input as the first (sublayers side by side),
     ``[S', T, hidden]``, added as well.  A norm that does not know one of these must refuse it.
+
+    A model with several residual streams (hyper-connections) keeps them in ``streams [N, T, hidden]`` (float32)
+    beside ``x``, which then holds the embedding's output: until the first update has been written
+    (``streams_unwritten``) every stream equals ``x``.  ``stream_update`` says how the pending output enters the
+    streams, ``(mix [N, N], share [N], mult)``: ``x_t = sum_s mix[s, t] x_s + mult * share[t] * pending``;
+    ``stream_read [N]`` are the weights of the sum that the next norm normalises (``None``: all ones, the model's
+    end).  The norm applies the update, writes the streams back and reads them in one kernel.
     """
 
     x: torch.Tensor
@@ -87,6 +94,10 @@ class Residual:
     rounded: torch.Tensor | None = None
     pending_bias: torch.Tensor | None = None
     pending_more: torch.Tensor | None = None
+    streams: torch.Tensor | None = None
+    streams_unwritten: bool = False
+    stream_update: tuple | None = None
+    stream_read: torch.Tensor | None = None
 
     def add(self, delta: torch.Tensor, scale: torch.Tensor | None = None, bias: torch.Tensor | None = None) -> None:
         if self.pending is not None:
@@ -103,6 +114,7 @@ class Residual:
 
     def clear(self) -> None:
         self.pending = self.pending_scale = self.pending_bias = self.pending_more = None
+        self.stream_update = self.stream_read = None
 
 
 @dataclass

@@ -18,11 +18,99 @@ class PreNormBlock(Block):
 
     capturable = True
 
+    def __init__(self, mixer, feed_forward, norms, *, prefix: str = "", hidden_size: int = 0, residual_mult: float = 1.0):
+        """``residual_mult``: a constant that every sublayer's output is multiplied by before it is added, ``x + m *
+        sublayer(norm(x))`` (1: the plain sum).  A layer may have no feed-forward (``prenorm_mixer_only``)."""
+        super().__init__(mixer, feed_forward, norms)
+        self.residual_mult, self.hidden = float(residual_mult), hidden_size
+        self.mult: torch.Tensor | None = None
+
+    def load(self, tensors) -> None:
+        super().load(tensors)
+        if self.residual_mult != 1.0:  # the norm that adds a pending output takes a factor per column
+            self.mult = torch.full((self.hidden,), self.residual_mult, dtype=torch.float32, device=self.mixer_norm.weight.device)
+
     def forward(self, state: Residual, ctx: StepContext, cache: LayerCache) -> None:
         h = self.mixer_norm.forward(state, ctx, ctx.dtype)
-        state.add(self.mixer.forward(h, ctx, cache))
-        h = self.feed_forward_norm.forward(state, ctx, ctx.dtype)
-        state.add(self.feed_forward.forward(h, ctx))
+        state.add(self.mixer.forward(h, ctx, cache), self.mult)
+        if self.feed_forward is not None:
+            h = self.feed_forward_norm.forward(state, ctx, ctx.dtype)
+            state.add(self.feed_forward.forward(h, ctx), self.mult)
+
+
+@register("block", "prenorm_mixer_only")
+class PreNormMixerOnlyBlock(PreNormBlock):
+    """The same arrangement for a layer without a feed-forward: one norm."""
+
+    NORMS = ("mixer",)
+
+
+@register("block", "hyper_prenorm")
+class HyperConnectionBlock(Block):
+    """Pre-norm sublayers on several residual streams ``x_1 .. x_N`` (hyper-connections) in the place of one.  Sublayer
+    ``q`` (the mixer, then the feed-forward) has learned ``read_q [N]``, ``mix_q [N, N]`` (indexed ``[from, to]``) and
+    ``share_q [N]``::
+
+        u = sum_s read_q[s] x_s        y = sublayer_q(norm_q(u))        x_t <- sum_s mix_q[s, t] x_s + m * share_q[t] * y
+
+    with all streams updated at once from the old ones and ``m`` a constant of the model (``residual_mult``).  At the
+    model's start every stream is the embedding's output; at its end the residual is the sum of the streams (the
+    final norm reads it with ``Residual.stream_read = None``).  The update that a sublayer's output is owed happens
+    inside the kernel of the norm that follows, together with that norm's read, in 32-bit."""
+
+    capturable = True
+
+    def __init__(self, mixer, feed_forward, norms, *, prefix: str, hidden_size: int, streams: int, names, residual_mult: float = 1.0):
+        """``names``: for ``"mixer"`` (and ``"feed_forward"``) the tensor names of ``read``, ``mix`` and ``share``
+        behind the layer's prefix."""
+        super().__init__(mixer, feed_forward, norms)
+        if not 1 <= streams <= 8:
+            raise ValueError(f"hyper_prenorm takes 1 to 8 residual streams, got {streams}")
+        wanted = {"mixer"} if feed_forward is None else {"mixer", "feed_forward"}
+        if set(names) != wanted or any(set(group) != {"read", "mix", "share"} for group in names.values()):
+            raise ValueError(f"hyper_prenorm wants the names of read, mix and share for {sorted(wanted)}")
+        self.count, self.hidden, self.mult = int(streams), hidden_size, float(residual_mult)
+        self.names = {sub: {key: prefix + name for key, name in group.items()} for sub, group in names.items()}
+        self.coefficients: dict[str, dict[str, torch.Tensor]] = {}
+
+    def weight_specs(self) -> list[WeightSpec]:
+        specs = super().weight_specs()
+        for group in self.names.values():  # the streams are 32-bit, and so is what multiplies them
+            specs += [
+                WeightSpec(group["read"], (self.count,), role="vector", init="ones_normal"),
+                WeightSpec(group["share"], (self.count,), role="vector", init="ones_normal"),
+                WeightSpec(group["mix"], (self.count, self.count), role="vector", init="small_normal"),
+            ]
+        return specs
+
+    def load(self, tensors) -> None:
+        super().load(tensors)
+        self.coefficients = {sub: {key: tensors[name] for key, name in group.items()} for sub, group in self.names.items()}
+
+    def _sublayer(self, which: str, norm, state: Residual, ctx: StepContext, run) -> None:
+        if state.streams is None:  # the model's first sublayer: the streams all equal the embedding's output
+            flat = ctx.buffer("residual.streams", (ctx.num_tokens, self.count * self.hidden), torch.float32)
+            state.streams = flat.view(self.count, ctx.num_tokens, self.hidden)  # stream after stream
+            state.streams_unwritten = True
+        elif state.streams.shape[0] != self.count:
+            raise ValueError("every layer of a model has the same number of residual streams")
+        held = self.coefficients[which]
+        state.stream_read = held["read"]
+        h = norm.forward(state, ctx, ctx.dtype)
+        state.add(run(h))
+        state.stream_update = (held["mix"], held["share"], self.mult)
+
+    def forward(self, state: Residual, ctx: StepContext, cache: LayerCache) -> None:
+        self._sublayer("mixer", self.mixer_norm, state, ctx, lambda h: self.mixer.forward(h, ctx, cache))
+        if self.feed_forward is not None:
+            self._sublayer("feed_forward", self.feed_forward_norm, state, ctx, lambda h: self.feed_forward.forward(h, ctx))
+
+
+@register("block", "hyper_prenorm_mixer_only")
+class HyperConnectionMixerOnlyBlock(HyperConnectionBlock):
+    """The same arrangement for a layer without a feed-forward: one norm."""
+
+    NORMS = ("mixer",)
 
 
 class _LayerScales:

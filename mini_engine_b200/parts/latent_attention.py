@@ -47,17 +47,27 @@ class LatentAttention(Mixer):
         rot_dim: int,
         value_dim: int,
         kv_rank: int,
-        q_rank: int,
+        q_rank: int | None,
         norm_eps: float,
         scale: float | None = None,
         window: int | None = None,
         position_encoding: PartSpec | None = None,
         head_gate: bool = False,
         names: Mapping[str, str] | None = None,
+        rotary_layout: str = "half",
     ):
         """``head_dim``: plain query/key elements per head; ``rot_dim``: rotated ones (0: none); ``position_encoding``
-        must be a rotate-half rotation over at most ``rot_dim`` elements (or ``None``: the part is used as it is)."""
-        if min(num_heads, head_dim, value_dim, kv_rank, q_rank) < 1 or rot_dim < 0:
+        must be a rotate-half rotation over at most ``rot_dim`` elements (or ``None``: the part is used as it is).
+        ``q_rank=None``: the queries have no latent of their own, ``q = W_q x`` (tensor ``q``).  ``rotary_layout``
+        ``"interleaved"``: the checkpoint pairs element ``2 i`` of a rotated part with ``2 i + 1``; the rows of the
+        query and key projections that make the rotated parts are then reordered once, when they are loaded, to
+        ``[even elements | odd elements]``: the same permutation on both sides leaves every score as it was, and the
+        kernels rotate halves."""
+        if rotary_layout not in ("half", "interleaved"):
+            raise ValueError(f"rotary_layout is 'half' or 'interleaved', got {rotary_layout!r}")
+        self.interleaved = rotary_layout == "interleaved"
+        q_rank = int(q_rank or 0)
+        if min(num_heads, head_dim, value_dim, kv_rank) < 1 or rot_dim < 0 or q_rank < 0:
             raise ValueError("latent_attention: sizes must be positive (rot_dim may be 0)")
         if value_dim > 512 or kv_rank > 512 or kv_rank + rot_dim > 2048:
             raise ValueError("latent_attention: kv_rank and value_dim up to 512, kv_rank + rot_dim up to 2048")
@@ -75,7 +85,7 @@ class LatentAttention(Mixer):
         defaults = {
             "dq": "q_down.weight", "q_norm": "q_norm.weight", "uq": "q_up.weight", "dkv": "kv_down.weight",
             "kv_norm": "kv_norm.weight", "uk": "k_up.weight", "uv": "v_up.weight", "gate": "gate_proj.weight",
-            "o": "o_proj.weight",
+            "o": "o_proj.weight", "q": "q_proj.weight",
         }  # fmt: skip
         self.names = {key: prefix + (names or {}).get(key, value) for key, value in defaults.items()}
         self.down: Linear | None = None
@@ -94,6 +104,8 @@ class LatentAttention(Mixer):
             WeightSpec(n["dq"], (self.q_rank, self.hidden)),
             WeightSpec(n["q_norm"], (self.q_rank,), role="vector", init="ones_normal"),
             WeightSpec(n["uq"], (heads * (self.dim + self.rot_dim), self.q_rank)),
+        ] if self.q_rank else [WeightSpec(n["q"], (heads * (self.dim + self.rot_dim), self.hidden))]
+        specs += [
             WeightSpec(n["dkv"], (self.kv_rank + self.rot_dim, self.hidden)),
             WeightSpec(n["kv_norm"], (self.kv_rank,), role="vector", init="ones_normal"),
             WeightSpec(n["uk"], (heads * self.dim, self.kv_rank)),
@@ -106,13 +118,20 @@ class LatentAttention(Mixer):
 
     def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
         n = self.names
-        rows = [tensors[n["dq"]], tensors[n["dkv"]]]
+        down_kv, up_q = tensors[n["dkv"]], tensors[n["uq"] if self.q_rank else n["q"]]
+        if self.interleaved and self.position is not None:
+            dims = self.position.rotary_dim
+            order = torch.cat((torch.arange(0, dims, 2), torch.arange(1, dims, 2), torch.arange(dims, self.rot_dim))).to(up_q.device)
+            per_head = up_q.view(self.heads, self.dim + self.rot_dim, -1)
+            up_q = torch.cat((per_head[:, : self.dim], per_head[:, self.dim :][:, order]), dim=1).reshape(up_q.shape).contiguous()
+            down_kv = torch.cat((down_kv[: self.kv_rank], down_kv[self.kv_rank :][order]), dim=0).contiguous()
+        rows = ([tensors[n["dq"]]] if self.q_rank else []) + [down_kv]
         if self.head_gate:
             rows.append(tensors[n["gate"]])
-        self.down = Linear(torch.cat(rows, dim=0).contiguous())
-        self.up_q = Linear(tensors[n["uq"]])
+        self.down = Linear(torch.cat(rows, dim=0).contiguous() if len(rows) > 1 else rows[0])
+        self.up_q = Linear(up_q)  # without a query latent: the query projection itself
         self.out = Linear(tensors[n["o"]])
-        self.q_norm, self.kv_norm = tensors[n["q_norm"]], tensors[n["kv_norm"]]
+        self.q_norm, self.kv_norm = (tensors[n["q_norm"]] if self.q_rank else None), tensors[n["kv_norm"]]
         # U_k as stored is [heads][dim][kv_rank]: the map from a head's plain query to the latent's space.
         self.key_maps = tensors[n["uk"]].view(self.heads, self.dim, self.kv_rank)
         # U_v as stored is [heads][value_dim][kv_rank]; the kernel walks the inner index first.
@@ -129,14 +148,14 @@ class LatentAttention(Mixer):
         if self.position is not None and table is None:
             raise ValueError("latent_attention takes a rotation that its kernels apply, or none")
         down = self.down.forward(h, ctx, "latent.down")
-        q_latent = ctx.buffer("latent.q_latent", (tokens, self.q_rank), ctx.dtype)
+        q_latent = ctx.buffer("latent.q_latent", (tokens, self.q_rank), ctx.dtype) if self.q_rank else None
         gate = ctx.buffer("latent.gate", (tokens, heads), torch.float32) if self.head_gate else None
         ops.latent_down_finish(
             down=down, q_rank=self.q_rank, kv_rank=self.kv_rank, rot_dim=self.rot_dim, q_weight=self.q_norm,
             kv_weight=self.kv_norm, eps=self.eps, cos_sin=table, slot_mapping=ctx.slot_mapping[cache.group],
             q_latent=q_latent, k_pages=cache.k, gates=heads if self.head_gate else 0, gate_out=gate,
         )  # fmt: skip
-        q_parts = self.up_q.forward(q_latent, ctx, "latent.q")
+        q_parts = self.up_q.forward(q_latent if self.q_rank else h, ctx, "latent.q")
         q = ctx.buffer("latent.q_mapped", (tokens, heads * key_width), ctx.dtype)
         ops.head_product(q_parts, self.key_maps, q, tail=self.rot_dim, cos_sin=table)
         mean = ctx.buffer("latent.mean", (tokens, heads * self.kv_rank), ctx.dtype)

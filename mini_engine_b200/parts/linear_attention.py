@@ -15,16 +15,23 @@ the recurrence and the unit norm are computed in 32-bit from the 32-bit sums of 
 The five projections of the input run as one product on the row-concatenated weight; the second,
 small factor of the decay's low-rank projection is applied by the kernel that prepares q, k and the
 decays of all tokens for the scan.
+
+``retention`` is the same recurrence with a fixed decay per head in the place of the data-dependent one, ``S_t = a_h
+S_(t-1) + k_t v_t^T``: q and k are rotated by position (rotate-half, on their first ``rotary_dim`` elements), k is
+multiplied by ``dim^-1/2`` after its rotation, there are no biases and no decay projection; each head's ``o_t`` is divided
+by its root mean square (no weight), multiplied by ``silu(W_g h_t)`` and projected.  It shares the scan and the finishing
+kernel with the gated form; a kernel of its own rotates, scales and lays q, k and the decays out for the scan.
 """
 
 from __future__ import annotations
 
-from typing import Mapping
+from typing import Mapping, Sequence
 
 import torch
 
 from mini_engine_b200.csrc import ops
-from mini_engine_b200.parts.base import LayerCache, Mixer, StateSpec, StepContext, register
+from mini_engine_b200.config.model_spec import PartSpec
+from mini_engine_b200.parts.base import LayerCache, Mixer, StateSpec, StepContext, build_part, register
 from mini_engine_b200.parts.linear import Linear
 from mini_engine_b200.weights.loader import WeightSpec
 
@@ -111,3 +118,88 @@ class GatedLinearAttention(Mixer):
             heads=self.heads, vdim=self.vdim,
         )  # fmt: skip
         return self.out.forward(gated, ctx, "gla.o")
+
+
+@register("mixer", "retention")
+class Retention(Mixer):
+    capturable = True
+    programmatic_launch = False  # it shares the scan kernel of the gated form, whose steps run in plain stream order
+
+    def __init__(
+        self,
+        prefix: str,
+        hidden_size: int,
+        *,
+        num_heads: int,
+        head_dim: int,
+        value_dim: int,
+        decay: Sequence[float],
+        norm_eps: float,
+        position_encoding: PartSpec | None = None,
+        key_scale: float | None = None,
+        names: Mapping[str, str] | None = None,
+    ):
+        """``decay``: one constant per head, ``0 < a_h <= 1``; ``key_scale``: what rotated keys are multiplied by
+        (default ``head_dim ** -0.5``); ``position_encoding``: a rotate-half rotation that the kernel applies, or none."""
+        if min(num_heads, head_dim, value_dim) < 1:
+            raise ValueError("retention: sizes must be positive")
+        if len(decay) != num_heads or not all(0.0 < float(a) <= 1.0 for a in decay):
+            raise ValueError(f"retention: one decay in (0, 1] per head ({num_heads}), got {list(decay)}")
+        self.hidden, self.heads, self.dim, self.vdim = hidden_size, num_heads, head_dim, value_dim
+        self.decay_values, self.eps = [float(a) for a in decay], float(norm_eps)
+        self.k_scale = float(key_scale) if key_scale is not None else head_dim**-0.5
+        self.position = None
+        if position_encoding is not None:
+            self.position = build_part("position_encoding", position_encoding, prefix, hidden_size)
+        defaults = {"q": "q_proj.weight", "k": "k_proj.weight", "v": "v_proj.weight", "g": "g_proj.weight", "o": "o_proj.weight"}
+        self.names = {key: prefix + (names or {}).get(key, value) for key, value in defaults.items()}
+        widths = {"q": num_heads * head_dim, "k": num_heads * head_dim, "v": num_heads * value_dim, "g": num_heads * value_dim}
+        self.columns, column = {}, 0
+        for key, width in widths.items():  # columns of the fused input projection, in this order
+            self.columns[key] = column
+            column += width
+        self.proj: Linear | None = None
+        self.out: Linear | None = None
+        self.decay: torch.Tensor | None = None
+
+    def state(self) -> StateSpec:
+        return StateSpec((self.heads, self.dim, self.vdim), torch.float32)
+
+    def weight_specs(self) -> list[WeightSpec]:
+        n, inner, outer = self.names, self.heads * self.dim, self.heads * self.vdim
+        specs = [
+            WeightSpec(n["q"], (inner, self.hidden)),
+            WeightSpec(n["k"], (inner, self.hidden)),
+            WeightSpec(n["v"], (outer, self.hidden)),
+            WeightSpec(n["g"], (outer, self.hidden)),
+            WeightSpec(n["o"], (self.hidden, outer)),
+        ]
+        return specs + (self.position.weight_specs() if self.position is not None else [])
+
+    def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
+        n = self.names
+        self.proj = Linear(torch.cat([tensors[n[key]] for key in ("q", "k", "v", "g")], dim=0).contiguous())
+        self.out = Linear(tensors[n["o"]])
+        # a decay enters the recurrence: the float32 nearest to the configuration's number, made from the double
+        self.decay = torch.tensor(self.decay_values, dtype=torch.float64).to(torch.float32).to(tensors[n["q"]].device)
+        if self.position is not None:
+            self.position.load(tensors)
+
+    def forward(self, h: torch.Tensor, ctx: StepContext, cache: LayerCache) -> torch.Tensor:
+        tokens = h.shape[0]
+        table = self.position.step_angles(ctx) if self.position is not None else None
+        if self.position is not None and table is None:
+            raise ValueError("retention takes a rotation that its kernel applies, or none")
+        proj = self.proj.forward(h, ctx, "retention.proj")
+        raw = ctx.buffer("retention.raw", (tokens, self.heads * self.vdim), torch.float32)
+        prepared = ctx.buffer("retention.prepared", (tokens, self.heads * 3 * self.dim), torch.float32)
+        ops.retention_scan(
+            proj=proj, columns=self.columns, cos_sin=table, decay=self.decay, k_scale=self.k_scale, ctx=ctx,
+            state=cache.state, out=raw, prepared=prepared, heads=self.heads, dim=self.dim, vdim=self.vdim,
+        )  # fmt: skip
+        gated = ctx.buffer("retention.out", (tokens, self.heads * self.vdim), ctx.dtype)
+        ops.gla_finish(
+            o=raw, proj=proj, gate_column=self.columns["g"], weight=None, eps=self.eps, out=gated, heads=self.heads,
+            vdim=self.vdim,
+        )  # fmt: skip
+        return self.out.forward(gated, ctx, "retention.o")

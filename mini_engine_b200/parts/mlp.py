@@ -9,6 +9,9 @@ The gate has three constants for models whose gated unit differs: ``y = g * sigm
 (u + up_offset)`` with ``g = min(x Wg^T, limit)`` and ``u = clamp(x Wu^T, -limit, limit)`` when a
 ``limit`` is given.  Slope 1, no limit and offset 0 are SwiGLU.  ``activation="gelu_tanh"`` gates with
 ``0.5 g (1 + tanh(sqrt(2 / pi) (g + 0.044715 g^3)))`` in the place of ``g * sigmoid(gate_slope * g)``.
+
+``mlp`` is the feed-forward without a gate, ``y = act(x Wu^T) Wd^T`` with ``act`` the square of relu (``relu_squared``),
+``relu``, ``silu`` or ``gelu_tanh``: the up product's partial sums meet in the activation kernel, which rounds once.
 """
 
 from __future__ import annotations
@@ -17,6 +20,7 @@ from typing import Mapping
 
 import torch
 
+from mini_engine_b200.csrc import ops
 from mini_engine_b200.parts.base import FeedForward, StepContext, register
 from mini_engine_b200.parts.linear import GatedLinear, Linear
 from mini_engine_b200.weights.loader import WeightSpec
@@ -69,3 +73,37 @@ class GatedMLP(FeedForward):
     def forward(self, h: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         act = self.gate_up.forward(h, ctx, "mlp")
         return self.down.forward(act, ctx, "mlp.down")
+
+
+@register("feed_forward", "mlp")
+class PlainMLP(FeedForward):
+    capturable = True
+
+    def __init__(
+        self, prefix: str, hidden_size: int, *, intermediate_size: int, activation: str = "relu_squared",
+        names: Mapping[str, str] | None = None,
+    ):  # fmt: skip
+        if activation not in ops.PLAIN_ACTIVATIONS:
+            raise ValueError(f"mlp: activation must be one of {sorted(ops.PLAIN_ACTIVATIONS)}, got {activation!r}")
+        if intermediate_size < 1:
+            raise ValueError("mlp: the intermediate size must be positive")
+        self.hidden, self.inter, self.activation = hidden_size, intermediate_size, activation
+        defaults = {"up": "up_proj.weight", "down": "down_proj.weight"}
+        self.names = {key: prefix + (names or {}).get(key, value) for key, value in defaults.items()}
+        self.up: Linear | None = None
+        self.down: Linear | None = None
+
+    def weight_specs(self) -> list[WeightSpec]:
+        return [
+            WeightSpec(self.names["up"], (self.inter, self.hidden)),
+            WeightSpec(self.names["down"], (self.hidden, self.inter)),
+        ]
+
+    def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
+        self.up, self.down = Linear(tensors[self.names["up"]]), Linear(tensors[self.names["down"]])
+
+    def forward(self, h: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        sums = self.up.forward(h, ctx, "mlp.up")
+        act = ctx.buffer("mlp.plain_act", (h.shape[0], self.inter), h.dtype)
+        ops.activation(sums, act, self.activation)
+        return self.down.forward(act, ctx, "mlp.plain_down")

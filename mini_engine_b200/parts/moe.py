@@ -7,6 +7,10 @@ weight_scale``.  Unit ``e``: ``g = min(W_gate h, limit)``, ``u = clamp(W_up h, -
 sigmoid(gate_slope * g) * (u + up_offset))`` (the constants of :mod:`~mini_engine_b200.parts.mlp`).  The output is
 the weighted sum of the chosen units' outputs.
 
+Options: ``router_bias`` adds a learned number per unit to ``W_r h``; ``scoring="softmax_chosen"`` chooses the ``top``
+units with the largest logits and weighs them by the softmax over the chosen logits only; ``shared_intermediate_size``
+adds a gated unit of that width (tensors ``shared``) that runs for every token, its output added with weight one.
+
 How it runs, two forms; neither has a shape that depends on the choice, so both can be captured in a graph, and in
 both a token's result does not depend on the rest of the batch.
 
@@ -31,7 +35,7 @@ import torch
 
 from mini_engine_b200.csrc import ops
 from mini_engine_b200.parts.base import FeedForward, StepContext, register
-from mini_engine_b200.parts.linear import Linear
+from mini_engine_b200.parts.linear import GatedLinear, Linear
 from mini_engine_b200.weights.loader import WeightSpec
 
 # From this many tokens on a bfloat16 step sorts its rows by unit and computes only chosen units.  Below, the
@@ -58,7 +62,16 @@ class RoutedExperts(FeedForward):
         limit: float | None = None,
         up_offset: float = 0.0,
         names: Mapping[str, str] | None = None,
+        router_bias: bool = False,
+        scoring: str = "sigmoid",
+        shared_intermediate_size: int | None = None,
     ):
+        if scoring not in ops.ROUTE_SCORINGS:
+            raise ValueError(f"routed_experts: scoring must be one of {sorted(ops.ROUTE_SCORINGS)}, got {scoring!r}")
+        self.router_bias, self.scoring = bool(router_bias), scoring
+        self.shared_inter = int(shared_intermediate_size or 0)
+        if self.shared_inter < 0:
+            raise ValueError("routed_experts: the shared unit's width must be positive")
         if min(units, top, intermediate_size, group_count, group_keep) < 1:
             raise ValueError("routed_experts: sizes must be positive")
         if units % group_count or group_keep > group_count or top > group_keep * (units // group_count):
@@ -71,12 +84,16 @@ class RoutedExperts(FeedForward):
         self.group_count, self.group_keep, self.weight_scale = group_count, group_keep, float(weight_scale)
         self.gate_slope, self.limit, self.up_offset = float(gate_slope), limit, float(up_offset)
         defaults = {"router": "router.weight", "unit": "experts.{index}.", "gate": "gate_proj.weight",
-                    "up": "up_proj.weight", "down": "down_proj.weight"}  # fmt: skip
+                    "up": "up_proj.weight", "down": "down_proj.weight", "router_bias": "router.bias",
+                    "shared": "shared_expert."}  # fmt: skip
         self.names = {key: (names or {}).get(key, value) for key, value in defaults.items()}
         self.prefix = prefix
         self.gate_up: Linear | None = None
         self.down: Linear | None = None
         self.router: torch.Tensor | None = None
+        self.bias: torch.Tensor | None = None
+        self.shared_gate_up: GatedLinear | None = None
+        self.shared_down: Linear | None = None
         self.sorted_gate_up = self.sorted_down = None  # plans of the grouped products, when the sizes allow them
 
     def _name(self, unit: int, which: str) -> str:
@@ -92,6 +109,15 @@ class RoutedExperts(FeedForward):
             ]
         # the router is applied in 32-bit
         specs.append(WeightSpec(self.prefix + self.names["router"], (self.units, self.hidden), role="vector", init="small_normal"))
+        if self.router_bias:
+            specs.append(WeightSpec(self.prefix + self.names["router_bias"], (self.units,), role="vector", init="small_normal"))
+        if self.shared_inter:
+            shared = self.prefix + self.names["shared"]
+            specs += [
+                WeightSpec(shared + self.names["gate"], (self.shared_inter, self.hidden)),
+                WeightSpec(shared + self.names["up"], (self.shared_inter, self.hidden)),
+                WeightSpec(shared + self.names["down"], (self.hidden, self.shared_inter)),
+            ]
         return specs
 
     def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
@@ -100,6 +126,15 @@ class RoutedExperts(FeedForward):
         self.gate_up = Linear(torch.cat(gates + ups, dim=0).contiguous())  # [all gates | all ups]
         self.down = Linear(torch.cat([tensors[self._name(unit, "down")] for unit in range(self.units)], dim=1).contiguous())
         self.router = tensors[self.prefix + self.names["router"]]
+        if self.router_bias:
+            self.bias = tensors[self.prefix + self.names["router_bias"]]
+        if self.shared_inter:
+            shared = self.prefix + self.names["shared"]
+            self.shared_gate_up = GatedLinear(
+                torch.cat((tensors[shared + self.names["gate"]], tensors[shared + self.names["up"]]), dim=0).contiguous(),
+                slope=self.gate_slope, limit=self.limit, offset=self.up_offset,
+            )  # fmt: skip
+            self.shared_down = Linear(tensors[shared + self.names["down"]])
         if gates[0].dtype == torch.bfloat16 and ops.tensor_core_gemm_supports(self.inter, self.hidden) and ops.tensor_core_gemm_supports(self.hidden, self.inter):
             # unit after unit: [gate rows; up rows] of each, and the down matrices stacked by rows
             stacked = torch.cat([torch.cat((gate, up), dim=0) for gate, up in zip(gates, ups)], dim=0).contiguous()
@@ -113,8 +148,20 @@ class RoutedExperts(FeedForward):
         chosen_weight = ctx.buffer("routed.chosen_weight", (tokens, self.top), torch.float32)
         ops.route(
             h=h, router=self.router, weights=weights, chosen=chosen, chosen_weight=chosen_weight, top=self.top,
-            group_count=self.group_count, group_keep=self.group_keep, weight_scale=self.weight_scale,
+            group_count=self.group_count, group_keep=self.group_keep, weight_scale=self.weight_scale, bias=self.bias,
+            scoring=self.scoring,
         )  # fmt: skip
+        routed = self._forward_routed(h, ctx, chosen, chosen_weight, weights)
+        if not self.shared_inter:
+            return routed
+        act = self.shared_gate_up.forward(h, ctx, "routed.shared")
+        shared = self.shared_down.forward(act, ctx, "routed.shared_down")
+        out = ctx.buffer("routed.sum", (tokens, self.hidden), torch.float32)
+        ops.branch_sum([(routed, 1.0), (shared, 1.0)], out)  # each output whole before the two meet
+        return out.unsqueeze(0)
+
+    def _forward_routed(self, h: torch.Tensor, ctx: StepContext, chosen, chosen_weight, weights) -> torch.Tensor:
+        tokens = h.shape[0]
         # Many tokens: only chosen units are computed.  Very few: only chosen units' weights are read.  The choice
         # depends on the token count alone, so a captured step always takes the form it was captured with.
         if self.sorted_gate_up is not None and (tokens >= SORTED_MIN_TOKENS or 2 * tokens * self.top <= self.units):

@@ -53,12 +53,34 @@ class RMSNorm(Norm):
             raise ValueError("rmsnorm adds one pending output without a bias")
         count = state.x.shape[0] if rows is None else rows.shape[0]
         out = ctx.buffer("norm.out" if rows is None else "norm.rows", (count, self.dim), out_dtype)
+        if state.streams is not None:
+            return self._forward_streams(state, out, rows, residual_scale, keep_normed)
         ops.add_rmsnorm(
             state.x, state.pending, self.weight, self.eps, out, rows, state.pending_scale, residual_scale, keep_normed
         )
         if rows is None:
             state.clear()
             state.rounded = out if keep_normed else None  # with keep_normed, `out` is the new stream, rounded
+        return out
+
+
+    def _forward_streams(self, state: Residual, out, rows, residual_scale, keep_normed) -> torch.Tensor:
+        """Several residual streams: the pending output's update of all streams, their weighted sum and its norm are
+        one kernel (see :class:`~mini_engine_b200.parts.base.Residual`)."""
+        if residual_scale != 1.0 or keep_normed or state.pending_scale is not None:
+            raise ValueError("rmsnorm over several residual streams stands in front of its sublayer: no factor, no scale, no write-back")
+        if (state.pending is None) != (state.stream_update is None):
+            raise RuntimeError("a pending output of a model with several streams comes with its update, and only with it")
+        mix, share, mult = state.stream_update or (None, None, 1.0)
+        ops.hyper_step(
+            streams=state.streams, seed=state.x if state.streams_unwritten else None, pending=state.pending, mix=mix,
+            share=share, mult=mult, read=state.stream_read, weight=self.weight, eps=self.eps, out=out, rows=rows,
+        )  # fmt: skip
+        if rows is None:
+            if state.pending is not None:
+                state.streams_unwritten = False
+            state.clear()
+            state.rounded = None
         return out
 
 
