@@ -79,7 +79,7 @@ class HyperConnectionBlock(Block):
             specs += [
                 WeightSpec(group["read"], (self.count,), role="vector", init="ones_normal"),
                 WeightSpec(group["share"], (self.count,), role="vector", init="ones_normal"),
-                WeightSpec(group["mix"], (self.count, self.count), role="vector", init="small_normal"),
+                WeightSpec(group["mix"], (self.count, self.count), role="vector", init="eye_normal"),
             ]
         return specs
 

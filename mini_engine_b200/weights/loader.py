@@ -54,7 +54,8 @@ class WeightSpec:
     shape: tuple[int, ...]
     role: str = "matrix"  # "matrix", "vector" or "table"
     # random-weights mode: "normal" (N(0, 0.02)), "ones_normal" (1 + N(0, 0.1)), "small_normal" (N(0, 0.1),
-    # weights kept around zero), "wide_normal" (N(0, 1)) or "positive" (0.05 + |N(0, 0.1)|)
+    # weights kept around zero), "wide_normal" (N(0, 1)), "positive" (0.05 + |N(0, 0.1)|) or "eye_normal" (a matrix,
+    # identity + N(0, 0.1))
     init: str = "normal"
     alias_of: str | None = None  # tied tensor: use that tensor's storage; a stored copy is ignored
     optional: bool = False  # a tensor that a checkpoint may carry although this model has no use for it: never loaded

@@ -84,6 +84,9 @@ def random_tensor(spec: WeightSpec, seed: int, dtype: torch.dtype, device="cpu",
         values = values + 1.0
     elif spec.init == "small_normal":
         values = values * NORM_STD
+    elif spec.init == "eye_normal":  # a square matrix around the identity (what mixes residual streams)
+        values = values * NORM_STD
+        values = values + torch.eye(spec.shape[0], spec.shape[1], dtype=values.dtype, device=values.device)
     elif spec.init == "wide_normal":
         pass  # N(0, 1): numbers that stand beside attention scores (a learned sink)
     elif spec.init == "positive":

@@ -140,9 +140,25 @@ def route(h, w, p, top):
     return best.indices, torch.softmax(best.values, dim=-1)
 
 
-def routed_feed_forward(h, w, p, mlp, choice=None):
-    """``choice``: (units, weights) to use in the place of this function's own routing."""
-    units, weights = choice if choice is not None else route(h, w, p, mlp["router"]["top"])
+def route_following(h, w, p, top, follow, close):
+    """The routing of :func:`route`, except that a token whose decision was won by less than ``close`` (in logits)
+    takes the units of ``follow [T, top]`` (another implementation's choice, which rounding may have turned)."""
+    logits = h @ w[p + "router"].T + w[p + "router.b"]
+    ranked = torch.sort(logits, dim=-1, descending=True).values
+    units, weights = route(h, w, p, top)
+    if logits.shape[-1] == top:
+        return units, weights
+    for t in range(h.shape[0]):
+        theirs = sorted(int(u) for u in follow[t])
+        if sorted(units[t].tolist()) != theirs and float(ranked[t, top - 1] - ranked[t, top]) < close:
+            units[t] = torch.tensor(theirs)
+            weights[t] = torch.softmax(logits[t, units[t]], dim=-1)
+    return units, weights
+
+
+def routed_feed_forward(h, w, p, mlp, follow=None, close=0.0):
+    top = mlp["router"]["top"]
+    units, weights = route(h, w, p, top) if follow is None else route_following(h, w, p, top, follow, close)
     out = torch.zeros_like(h)
     for t in range(h.shape[0]):
         for unit, weight in zip(units[t].tolist(), weights[t]):
@@ -152,8 +168,8 @@ def routed_feed_forward(h, w, p, mlp, choice=None):
     return out
 
 
-def feed_forward(h, w, p, mlp):
-    return dense_feed_forward(h, w, p) if mlp["kind"] == "dense" else routed_feed_forward(h, w, p, mlp)
+def feed_forward(h, w, p, mlp, follow=None, close=0.0):
+    return dense_feed_forward(h, w, p) if mlp["kind"] == "dense" else routed_feed_forward(h, w, p, mlp, follow, close)
 
 
 def mixer(layer, h, w, p, eps):
@@ -185,17 +201,19 @@ def hyper_sublayer(streams, w, p, mult, eps, norm_weight, sublayer):
     return torch.einsum("sr,stw->rtw", w[p + "mix"], streams) + mult * w[p + "out"].view(-1, 1, 1) * y
 
 
-def forward(config, w, tokens, return_layers=False):
-    """Logits ``[T, vocab]`` of one whole sequence (and the stream after every layer run)."""
+def forward(config, w, tokens, return_layers=False, follow=None, close=0.0):
+    """Logits ``[T, vocab]`` of one whole sequence (and the stream after every layer run).  ``follow``: per layer run
+    with routed units, another implementation's choices ``[T, top]``, taken where a decision was closer than ``close``."""
     eps, mult = config["norm"]["eps"], config.get("residual_mult", 1.0)
     x = w["embed"][torch.as_tensor(tokens, dtype=torch.long)]
     count = config.get("streams")
     streams = x.unsqueeze(0).repeat(count, 1, 1) if count else None
     after = []
-    for index in layer_order(config):
+    for run, index in enumerate(layer_order(config)):
         layer, name = config["layers"][index], f"l{index}."
+        theirs = None if follow is None else follow.get(run)
         mix = lambda h: mixer(layer, h, w, name + "mix.", eps)  # noqa: E731
-        ff = lambda h: feed_forward(h, w, name + "mlp.", layer["mlp"])  # noqa: E731
+        ff = lambda h: feed_forward(h, w, name + "mlp.", layer["mlp"], theirs, close)  # noqa: E731
         if streams is None:
             x = x + mult * mix(rms_norm(x, w[name + "norm1"], eps))
             if layer.get("mlp") is not None:
