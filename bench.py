@@ -5,6 +5,7 @@
     python bench.py --design pimezen      (another workload: that design beside Qwen3 dense at equal layer sizes)
     python bench.py --design molotar      (the same for the Molotar design)
     python bench.py --design bevadra      (the same for the Bevadra design)
+    python bench.py --design bizurax      (the same for the Bizurax design)
 
 The default run builds the Qwen3-8B layer sizes with seeded random bfloat16 weights, fills the
 cache of 8 requests with 2,048-token contexts, and times K decode steps (one token for every
@@ -646,7 +647,7 @@ def main() -> int:
     parser.add_argument("--fp32-check", type=int, default=256, metavar="TOKENS",
                         help="also run a prompt of this many tokens through the true 32-bit path of the same model and "
                              "compare the bfloat16 logits with it (0: skip; needs 33 GB more device memory for a second)")
-    parser.add_argument("--design", choices=["pimezen", "molotar", "bevadra"], default=None,
+    parser.add_argument("--design", choices=["pimezen", "molotar", "bevadra", "bizurax"], default=None,
                         help="instead of the default workload: prefill and decode of this design beside Qwen3 dense at equal "
                              "layer sizes, with every kernel class against its roofline (mini_engine_b200/cli/design_bench.py)")
     parser.add_argument("--design-sizes", default="1b,8b", help="layer sizes of the --design comparison")

@@ -1,7 +1,7 @@
-"""Prefill and decode throughput of another design (Pimezen, Molotar, Bevadra) beside Qwen3 dense at equal layer sizes.
+"""Prefill and decode throughput of another design (Pimezen, Molotar, Bevadra, Bizurax) beside Qwen3 dense at equal layer sizes.
 
-    python -m mini_engine_b200.cli.design_bench [--design pimezen|molotar|bevadra] [--sizes 1b,8b] [--steps K] [--warmup W]
-    (or: bench.py --design pimezen|molotar|bevadra)
+    python -m mini_engine_b200.cli.design_bench [--design pimezen|molotar|bevadra|bizurax] [--sizes 1b,8b] [--steps K] [--warmup W]
+    (or: bench.py --design pimezen|molotar|bevadra|bizurax)
     python -m mini_engine_b200.cli.design_bench --design bevadra --sizes 8b --capture prompt|decode   (a few eager steps, for a profiler)
 
 For each size both models get the same width, feed-forward width, head counts, head size, layer count
@@ -23,6 +23,13 @@ Bevadra gets four layers in the order attention, latent attention, attention tha
 values, latent attention; its attention has Qwen3's head counts and head size and a window of 1,024 tokens; its latent
 attention has as many heads with 128 plain and 64 rotated query/key elements, values of 128, a key/value latent of 512
 and a query latent of three eighths of the width, and the same window; its feed-forward is as wide as Qwen3's.
+
+Bizurax gets four layers in the order attention, retention, latent attention, retention, on four residual streams; its
+attention has Qwen3's head counts and head size, no window, scores capped at 20 and a learned sink; its retention has as
+many heads with the key and value widths of Pimezen's linear attention; its latent attention has 128 plain and 64 rotated
+query/key elements, values of 128 and a latent of 512; the attention layers have a squared-relu feed-forward one and a
+half times as wide as Qwen3's (the same weights), the retention layers 8 routed units a quarter as wide of which a token
+uses 2, beside a shared unit half as wide (a token uses as many feed-forward weights as in Qwen3).
 """
 
 from __future__ import annotations
@@ -45,7 +52,9 @@ SIZES = {
 TIMED = ("biased_attention", "mixed_attention", "gla_scan", "gla_finish", "branch_sum", "paged_attention", "qk_norm_rope_store",
          "add_rmsnorm", "swiglu", "gemm_tensor_core", "gemm_tensor_core_swiglu", "embedding", "rglru", "route",
          "qk_wide_norm_rope_store", "pair_embedding", "round_rows", "gemm_tensor_core_grouped", "sort_by_unit", "gather_rows",
-         "combine_rows", "add_layernorm", "latent_down_finish", "head_product", "logits_finish")  # fmt: skip
+         "combine_rows", "add_layernorm", "latent_down_finish", "head_product", "logits_finish", "retention_scan", "hyper_step",
+         "activation", "qkv_rope_unit_store")  # fmt: skip
+STREAMS, ROUTED_UNITS, ROUTED_USED = 4, 8, 2
 LATENT_RANK, LATENT_ROT = 512, 64
 UNITS, UNITS_USED, UNIT_GROUPS, UNIT_GROUPS_KEPT = 8, 2, 4, 2
 RECURRENCE_BLOCK, RECURRENCE_TAPS = 128, 4
@@ -84,6 +93,24 @@ def bevadra_config(size: dict):
                                     "logit_softcap": 30.0, "layers": layers})  # fmt: skip
 
 
+def bizurax_config(size: dict):
+    from mini_engine_b200.config import BizuraxConfig
+
+    d, h, ff = size["head_dim"], size["heads"], size["ff"]
+    attention = {"heads": h, "kv_heads": size["kv_heads"], "dim": d, "vdim": d, "scale": 10.0 / d, "softcap": 20.0,
+                 "rot": {"base": 250000.0, "dims": d, "scaling": {"factor": 4.0}}}  # fmt: skip
+    retention = {"heads": h, "dim": size["lin_dim"], "vdim": size["lin_vdim"], "decay": [1.0 - 2.0 ** (-5 - 6 * i / h) for i in range(h)],
+                 "rot": {"base": 1e6, "dims": size["lin_dim"]}}  # fmt: skip
+    latent = {"heads": h, "dim": d, "rot_dim": LATENT_ROT, "vdim": d, "kv_rank": LATENT_RANK, "scale": (d + LATENT_ROT) ** -0.5,
+              "rot": {"base": 1e4, "dims": LATENT_ROT}}  # fmt: skip
+    dense = {"kind": "dense", "ff": 3 * ff // 2}
+    routed = {"kind": "moe", "expert": {"ff": ff // 4}, "router": {"experts": ROUTED_UNITS, "top": ROUTED_USED}, "shared": {"ff": ff // 2}}
+    pattern = [("attention", attention, dense), ("retention", retention, routed), ("latent_attention", latent, dense), ("retention", retention, routed)]
+    layers = [{"type": kind, "mixer": mixer, "mlp": mlp} for kind, mixer, mlp in (pattern * size["layers"])[: size["layers"]]]
+    return BizuraxConfig.from_dict({"architecture": "Bizurax", "vocab": size["vocab"], "width": size["width"], "norm": {"eps": 1e-6},
+                                    "residual_mult": 0.5, "streams": STREAMS, "layers": layers})  # fmt: skip
+
+
 def configs(size: dict, design: str = "pimezen"):
     from mini_engine_b200.config import PimezenConfig, Qwen3Config
 
@@ -108,6 +135,8 @@ def configs(size: dict, design: str = "pimezen"):
         return {"molotar": molotar_config(size), "qwen3": qwen}
     if design == "bevadra":
         return {"bevadra": bevadra_config(size), "qwen3": qwen}
+    if design == "bizurax":
+        return {"bizurax": bizurax_config(size), "qwen3": qwen}
     return {"pimezen": pimezen, "qwen3": qwen}
 
 
@@ -231,6 +260,36 @@ def rooflines(design: str, size: dict, peaks: dict) -> dict:
         # kernel times are averaged over all layers, of which half have an attention and half a latent attention
         for name in [n for n in out if n.split(".")[1] in ("paged_attention", "latent_attention", "head_product")]:
             nbytes, nflops = out[name]["bytes"] * 0.5, out[name]["flops"] * 0.5
+            out[name] = {"bytes": nbytes, "flops": nflops, "roofline_us": max(nbytes / bw, nflops / flops) * 1e6}
+    elif design == "bizurax":
+        rank, rot, key = LATENT_RANK, LATENT_ROT, LATENT_RANK + LATENT_ROT
+        ld, lv = size["lin_dim"], size["lin_vdim"]
+        state, row = h * ld * lv * 4, (2 * h * ld + h * lv) * 4  # a request's state; a token's q, k and v sums (32-bit)
+        for phase, tokens, seen in (("prompt", PROMPT, seen_prompt), ("decode", BATCH, seen_decode)):
+            rows = tokens if phase == "prompt" else seen  # cached rows that the step reads at least once
+            bound(f"{phase}.latent_attention", (rows * key + tokens * h * (key + rank)) * 2, seen * h * 2 * (key + rank))
+            bound(f"{phase}.head_product", (2 * h * d * rank + tokens * h * (2 * d + rot + key + rank)) * 2, 2 * tokens * 2 * h * d * rank)
+            # the scan: the sums in, the rotated q, k and decays out and in again, the outputs, the state in and out
+            per_request = 1 if phase == "prompt" else BATCH
+            bound(f"{phase}.retention_scan", tokens * (row + 2 * 3 * h * ld * 4 + h * lv * 4) + per_request * 2 * state, tokens * h * ld * lv * 4)
+            # two norms per layer: every stream in and out, the pending output in, the normed row out
+            bound(f"{phase}.hyper_step", 2 * tokens * width * (2 * STREAMS * 4 + 4 + 2), 2 * tokens * width * 2 * STREAMS * STREAMS)
+        mixers = [width * (h * d + 2 * g * d) + h * d * width, width * (2 * h * ld + 2 * h * lv) + h * lv * width,
+                  width * (h * (d + rot) + key) + h * d * width, width * (2 * h * ld + 2 * h * lv) + h * lv * width]  # fmt: skip
+        mixer = sum(mixers) / len(mixers)
+        unit, shared, dense = 3 * width * (ff // 4), 3 * width * (ff // 2), 2 * width * (3 * ff // 2)
+        used = 0.5 * dense + 0.5 * (ROUTED_USED * unit + shared)
+        touched = 0.5 * dense + 0.5 * (ROUTED_UNITS * (1.0 - (1.0 - ROUTED_USED / ROUTED_UNITS) ** BATCH) * unit + shared)
+        held = 0.5 * dense + 0.5 * (ROUTED_UNITS * unit + shared)
+        for phase, tokens, nbytes in (("prompt", PROMPT, (mixer + held) * 2), ("decode", BATCH, (mixer + touched) * 2)):
+            nflops = 2 * tokens * (mixer + used)
+            out[f"{phase}.products"] = {"bytes": nbytes, "flops": nflops, "roofline_us": max(nbytes / bw, nflops / flops) * 1e6,
+                                        "kernels": ("gemm_tensor_core", "gemm_tensor_core_grouped", "gemm_tensor_core_swiglu", "swiglu", "activation")}  # fmt: skip
+        # kernel times are averaged over all layers: a quarter have an attention, a quarter a latent attention, half a retention
+        share = {"paged_attention": 0.25, "latent_attention": 0.25, "head_product": 0.25, "retention_scan": 0.5}
+        for name in [n for n in out if n.split(".")[1] in share]:
+            factor = share[name.split(".")[1]]
+            nbytes, nflops = out[name]["bytes"] * factor, out[name]["flops"] * factor
             out[name] = {"bytes": nbytes, "flops": nflops, "roofline_us": max(nbytes / bw, nflops / flops) * 1e6}
     elif design == "qwen3":
         mixer = width * (h * d + 2 * g * d) + h * d * width
@@ -409,7 +468,7 @@ def capture_steps(design: str, size_name: str, phase: str) -> None:
 
 def main(argv=None) -> int:
     parser = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
-    parser.add_argument("--design", choices=["pimezen", "molotar", "bevadra"], default="pimezen")
+    parser.add_argument("--design", choices=["pimezen", "molotar", "bevadra", "bizurax"], default="pimezen")
     parser.add_argument("--sizes", default="1b,8b")
     parser.add_argument("--steps", type=int, default=32)
     parser.add_argument("--warmup", type=int, default=5)

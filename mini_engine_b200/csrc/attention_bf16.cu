@@ -53,7 +53,17 @@ struct AttnParams {
     int gate_width = 1;           // 1: one multiplier per head; D: one per element
     const float* slopes = nullptr;       // [heads] slope_h of a distance bias slope_h * (p - j) taken off the scaled scores, or null
     const float* sink_values = nullptr;  // [heads] with sink: the silent participant's score (zero when null)
+    float cap_log2 = 0.0f;  // > 0: a scaled score s (log2 domain) becomes cap * tanh(s / cap); cap * log2(e) here
 };
+
+// The cap on a scaled score, both in the log2 domain (their quotient is the natural one).  The hardware's tanh is good
+// to about 2^-11 of its value, which on scores of a few units is below what bfloat16 probabilities resolve.
+__device__ __forceinline__ float capped_score(float s_log2, float cap_log2) {
+    if (cap_log2 <= 0.0f) return s_log2;
+    float t;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(__fdividef(s_log2, cap_log2)));
+    return cap_log2 * t;
+}
 
 // What the silent participant adds to a denominator that is relative to `max_log2` (scores in the log2 domain).
 __device__ __forceinline__ float sink_term(const AttnParams& p, float max_log2, int head) {
@@ -139,7 +149,8 @@ __device__ __forceinline__ void accumulate_pv(float (&acc)[D / 8][4], const floa
 template <int D, int KEYS>
 __device__ __forceinline__ void softmax_step(float (&s)[KEYS / 8][4], float (&acc)[D / 8][4], float (&row_max)[2],
                                              float (&row_sum)[2], const int (&row_pos)[2], int first_key,
-                                             int window, float scale_log2, int lane, const float (&row_slope)[2]) {
+                                             int window, float scale_log2, int lane, const float (&row_slope)[2],
+                                             float cap_log2 = 0.0f) {
     const int col0 = first_key + 2 * (lane & 3);
     float tile_max[2] = {-INFINITY, -INFINITY};
 #pragma unroll
@@ -149,7 +160,7 @@ __device__ __forceinline__ void softmax_step(float (&s)[KEYS / 8][4], float (&ac
             const int key = col0 + n * 8 + (i & 1);
             const int r = i >> 1;
             const bool visible = key <= row_pos[r] && (window <= 0 || key > row_pos[r] - window);
-            s[n][i] = visible ? s[n][i] * scale_log2 - row_slope[r] * static_cast<float>(row_pos[r] - key) : -INFINITY;
+            s[n][i] = visible ? capped_score(s[n][i] * scale_log2, cap_log2) - row_slope[r] * static_cast<float>(row_pos[r] - key) : -INFINITY;
             tile_max[r] = fmaxf(tile_max[r], s[n][i]);
         }
     float rescale[2], base[2];
@@ -263,7 +274,7 @@ __global__ void __launch_bounds__(ATTN_THREADS) attention_portions_kernel(AttnPa
         const __nv_bfloat16* k_tile = kv_tiles + s * 2 * BLOCK_KEYS * D;
         float scores[BLOCK_KEYS / 8][4];
         scores_tile<D, BLOCK_KEYS>(scores, q_frag, k_tile, lane);
-        softmax_step<D, BLOCK_KEYS>(scores, acc, row_max, row_sum, row_pos, tile * BLOCK_KEYS, p.window, p.scale_log2, lane, row_slope);
+        softmax_step<D, BLOCK_KEYS>(scores, acc, row_max, row_sum, row_pos, tile * BLOCK_KEYS, p.window, p.scale_log2, lane, row_slope, p.cap_log2);
         accumulate_pv<D, BLOCK_KEYS>(acc, scores, k_tile + BLOCK_KEYS * D, lane);
         __syncthreads();  // the next iteration's prefetch overwrites the other stage's reader
     }
@@ -402,7 +413,7 @@ __global__ void __launch_bounds__(ATTN_THREADS, 3) attention_decode_kernel(AttnP
         const int first_key = cta_start + t * DECODE_CHUNK + warp * KEYS;
         float scores[KEYS / 8][4];
         scores_tile<D, KEYS>(scores, q_frag, k_tile, lane);
-        softmax_step<D, KEYS>(scores, acc, row_max, row_sum, row_pos, first_key, p.window, p.scale_log2, lane, row_slope);
+        softmax_step<D, KEYS>(scores, acc, row_max, row_sum, row_pos, first_key, p.window, p.scale_log2, lane, row_slope, p.cap_log2);
         __syncwarp();  // every lane has read the keys: the next tile's keys may overwrite them
         if (more) issue(k_tile, p.k_pages, offset_next);
         cp_async_commit();
@@ -752,8 +763,8 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __g
             float prob[4];
 #pragma unroll
             for (int j = 0; j < 2; ++j) {
-                const float a = seen0 ? s[j] * p.scale_log2 - head_slope[j] * static_cast<float>(position - key0) : -INFINITY;
-                const float b = seen1 ? s[j + 2] * p.scale_log2 - head_slope[j] * static_cast<float>(position - key0 - 8) : -INFINITY;
+                const float a = seen0 ? capped_score(s[j] * p.scale_log2, p.cap_log2) - head_slope[j] * static_cast<float>(position - key0) : -INFINITY;
+                const float b = seen1 ? capped_score(s[j + 2] * p.scale_log2, p.cap_log2) - head_slope[j] * static_cast<float>(position - key0 - 8) : -INFINITY;
                 float tile_max = fmaxf(a, b);
                 tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, 4));
                 tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, 8));
@@ -949,13 +960,14 @@ ME_EXPORT int me_attention_portions_bf16(const void* q, const void* k_pages, con
                                          int entries, int max_new_tokens, int heads, int kv_heads, int head_dim,
                                          int page_size, int table_width, int window, const int* entry_ids,
                                          int sink, const float* gate, int gate_width, const float* slopes,
-                                         const float* sink_values, cudaStream_t stream) {
+                                         const float* sink_values, float softcap, cudaStream_t stream) {
     if (entries <= 0) return 0;
     if (!sizes_ok(head_dim, heads, kv_heads)) return ME_ERR_UNSUPPORTED;
     AttnParams p{static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(k_pages),
                  static_cast<const __nv_bfloat16*>(v_pages), block_table, cu_tokens, context_lens,
                  static_cast<__nv_bfloat16*>(out), nullptr, nullptr, entry_ids, scale * LOG2E, heads, kv_heads,
-                 page_size, table_width, window, 0, shift_of(page_size), 1, sink, gate, gate_width, slopes, sink_values};
+                 page_size, table_width, window, 0, shift_of(page_size), 1, sink, gate, gate_width, slopes, sink_values,
+                 softcap * LOG2E};
     return head_dim == 128 ? launch_portions<128>(p, entries, max_new_tokens, stream)
                            : launch_portions<64>(p, entries, max_new_tokens, stream);
 }
@@ -972,7 +984,7 @@ ME_EXPORT int me_attention_decode_bf16_tiled(const void* q, const void* k_pages,
                                              int tiles_per_cta, int heads, int kv_heads, int head_dim, int page_size,
                                              int table_width, int window, const int* entry_ids, int sink,
                                              const float* gate, int gate_width, const float* slopes,
-                                             const float* sink_values, cudaStream_t stream) {
+                                             const float* sink_values, float softcap, cudaStream_t stream) {
     if (entries <= 0) return 0;
     if (!sizes_ok(head_dim, heads, kv_heads) || heads / kv_heads > 16 || max_splits < 1) return ME_ERR_UNSUPPORTED;
     if (tiles_per_cta < 1 || tiles_per_cta > MAX_DECODE_TILES) return ME_ERR_ARGUMENT;
@@ -980,7 +992,7 @@ ME_EXPORT int me_attention_decode_bf16_tiled(const void* q, const void* k_pages,
                  static_cast<const __nv_bfloat16*>(v_pages), block_table, cu_tokens, context_lens,
                  static_cast<__nv_bfloat16*>(out), partials, counters, entry_ids, scale * LOG2E, heads, kv_heads,
                  page_size, table_width, window, max_splits, shift_of(page_size), tiles_per_cta, sink, gate, gate_width,
-                 slopes, sink_values};
+                 slopes, sink_values, softcap * LOG2E};
     return head_dim == 128 ? launch_decode<128>(p, entries, stream) : launch_decode<64>(p, entries, stream);
 }
 
@@ -996,7 +1008,8 @@ ME_EXPORT int me_attention_decode_bf16_tma(const void* k_map, const void* v_map,
                                            int* counters, float scale, int entries, int splits, int warps, int heads,
                                            int kv_heads, int head_dim, int page_size, int table_width, int window,
                                            const int* entry_ids, int sink, const float* gate, int gate_width,
-                                           const float* slopes, const float* sink_values, cudaStream_t stream) {
+                                           const float* slopes, const float* sink_values, float softcap,
+                                           cudaStream_t stream) {
     if (entries <= 0) return 0;
     if (!sizes_ok(head_dim, heads, kv_heads) || heads / kv_heads > 8) return ME_ERR_UNSUPPORTED;
     if (shift_of(page_size) < 3) return ME_ERR_UNSUPPORTED;
@@ -1004,7 +1017,8 @@ ME_EXPORT int me_attention_decode_bf16_tma(const void* k_map, const void* v_map,
     if (warps != 8 && warps != 6) return ME_ERR_ARGUMENT;
     AttnParams p{static_cast<const __nv_bfloat16*>(q), nullptr, nullptr, block_table, cu_tokens, context_lens,
                  static_cast<__nv_bfloat16*>(out), partials, counters, entry_ids, scale * LOG2E, heads, kv_heads,
-                 page_size, table_width, window, splits, shift_of(page_size), 0, sink, gate, gate_width, slopes, sink_values};
+                 page_size, table_width, window, splits, shift_of(page_size), 0, sink, gate, gate_width, slopes, sink_values,
+                 softcap * LOG2E};
     CUtensorMap maps[2];
     memcpy(&maps[0], k_map, sizeof(CUtensorMap));
     memcpy(&maps[1], v_map, sizeof(CUtensorMap));
@@ -1032,7 +1046,7 @@ ME_EXPORT int me_attention_decode_bf16(const void* q, const void* k_pages, const
                                        int page_size, int table_width, int window, cudaStream_t stream) {
     return me_attention_decode_bf16_tiled(q, k_pages, v_pages, block_table, cu_tokens, context_lens, out, partials,
                                           nullptr, scale, entries, max_splits, 1, heads, kv_heads, head_dim, page_size,
-                                          table_width, window, nullptr, 0, nullptr, 1, nullptr, nullptr, stream);
+                                          table_width, window, nullptr, 0, nullptr, 1, nullptr, nullptr, 0.0f, stream);
 }
 
 // ------------------------------------------------- decode attention without allocation

@@ -41,7 +41,7 @@ def _tc_library():
         import ctypes
 
         lib = load_library("attention_tcgen05")
-        lib.me_attention_tcgen05.argtypes = [c_void_p] * 7 + [c_float] + [c_int] * 7 + [c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p]
+        lib.me_attention_tcgen05.argtypes = [c_void_p] * 7 + [c_float] + [c_int] * 7 + [c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_float, c_void_p]
         lib.me_attention_tcgen05.restype = c_int
         lib.me_attention_take_error.argtypes = [ctypes.POINTER(c_int)]
         lib.me_attention_take_error.restype = c_int
@@ -113,11 +113,11 @@ def _library():
         import ctypes
 
         lib = load_library("attention_bf16")
-        lib.me_attention_portions_bf16.argtypes = [c_void_p] * 7 + [c_float] + [c_int] * 8 + [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p]
+        lib.me_attention_portions_bf16.argtypes = [c_void_p] * 7 + [c_float] + [c_int] * 8 + [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_float, c_void_p]
         lib.me_attention_portions_bf16.restype = c_int
-        lib.me_attention_decode_bf16_tiled.argtypes = [c_void_p] * 9 + [c_float] + [c_int] * 9 + [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p]
+        lib.me_attention_decode_bf16_tiled.argtypes = [c_void_p] * 9 + [c_float] + [c_int] * 9 + [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_float, c_void_p]
         lib.me_attention_decode_bf16_tiled.restype = c_int
-        lib.me_attention_decode_bf16_tma.argtypes = [c_void_p] * 9 + [c_float] + [c_int] * 9 + [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p]
+        lib.me_attention_decode_bf16_tma.argtypes = [c_void_p] * 9 + [c_float] + [c_int] * 9 + [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_float, c_void_p]
         lib.me_attention_decode_bf16_tma.restype = c_int
         lib.me_attention_bf16_take_error.argtypes = [ctypes.POINTER(c_int)]
         lib.me_attention_bf16_take_error.restype = c_int
@@ -189,7 +189,7 @@ def decode_splits(max_context_len: int, tiles_per_cta: int = 1) -> int:
 def paged_attention(q, k_pages, v_pages, block_table, ctx, out, heads, kv_heads, head_dim, scale, window,
                     decode_warps: int | None = None, decode_splits_per_pair: int | None = None, sink: bool = False,
                     gate: torch.Tensor | None = None, slopes: torch.Tensor | None = None,
-                    sink_values: torch.Tensor | None = None) -> None:
+                    sink_values: torch.Tensor | None = None, softcap: float = 0.0) -> None:
     """Attention of the batch's new tokens.  Entries that bring one token take the split decode
     kernel, the others a portions kernel; a step that holds both kinds is two launches, each over
     its own list of entries.  ``decode_warps`` (6 or 8) and ``decode_splits_per_pair`` pin the form
@@ -198,7 +198,8 @@ def paged_attention(q, k_pages, v_pages, block_table, ctx, out, heads, kv_heads,
     ``sink``: the softmax has one more participant of score zero and no value, or of the learned score
     ``sink_values[h]`` (float32 ``[heads]``); ``gate`` (float32 ``[T, heads]`` or ``[T, heads * head_dim]``): a
     multiplier on every head's output, or on every element; ``slopes`` (float32 ``[heads]``): ``slopes[h] * (p - j)``
-    is taken off the scaled score of query ``p`` and key ``j``.  Every kernel knows all of them."""
+    is taken off the scaled score of query ``p`` and key ``j``; ``softcap`` > 0: a scaled score ``s`` becomes ``softcap *
+    tanh(s / softcap)`` (before the distance bias).  Every kernel knows all of them."""
     for name, t in (("q", q), ("out", out), ("k_pages", k_pages), ("v_pages", v_pages)):
         if t.dtype != torch.bfloat16 or not t.is_contiguous():
             raise ops.KernelError(f"{name} must be contiguous bfloat16")
@@ -214,7 +215,7 @@ def paged_attention(q, k_pages, v_pages, block_table, ctx, out, heads, kv_heads,
             raise ops.KernelError(f"{name} must be contiguous float32 [heads]")
     sink_flag, gate_ptr = (1 if (sink or sink_values is not None) else 0), (None if gate is None else gate.data_ptr())
     options = (sink_flag, gate_ptr, gate_width, None if slopes is None else slopes.data_ptr(),
-               None if sink_values is None else sink_values.data_ptr())  # fmt: skip
+               None if sink_values is None else sink_values.data_ptr(), float(softcap or 0.0))  # fmt: skip
     stream = _ops_stream()
     page_size, width = k_pages.shape[2], block_table.shape[1]
     common = (q.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), block_table.data_ptr(), ctx.cu_tokens.data_ptr(),

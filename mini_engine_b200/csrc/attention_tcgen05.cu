@@ -61,6 +61,7 @@ struct TcAttnParams {
     const float* slopes;       // [heads] slope_h * (p - j) is taken off the scaled score, or null
     const float* sink_values;  // [heads] the silent participant's score (null with `sink`: zero)
     const float* gate;         // [tokens][heads * gate_width] multiplier of the output, or null
+    float cap_log2;            // > 0: a scaled score s (log2 domain) becomes cap * tanh(s / cap); cap * log2(e) here
 };
 
 // 2^x by the special-function unit alone (about 2 ulp; the result is rounded to bfloat16 anyway).
@@ -301,11 +302,22 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             if (OPT) {
                 // raw <- score * scale + slope * (key - position), in the exponent's base 2; -inf where masked
                 const float2 scale2 = make_float2(p.scale_log2, p.scale_log2), slope2 = make_float2(slope_log2, slope_log2);
+                const float cap_scale = p.cap_log2 > 0.0f ? p.scale_log2 / p.cap_log2 : 0.0f;  // score -> tanh's argument
+                const float2 cap2 = make_float2(p.cap_log2, p.cap_log2), cap_scale2 = make_float2(cap_scale, cap_scale);
                 float2 distance = make_float2(static_cast<float>(first_key - row_pos), static_cast<float>(first_key + 1 - row_pos));
                 const int lowest_seen = p.window > 0 ? row_pos - p.window + 1 : 0;
 #pragma unroll
                 for (int i = 0; i < 64; i += 2) {
-                    float2 x = __ffma2_rn(make_float2(__uint_as_float(raw[i]), __uint_as_float(raw[i + 1])), scale2, __fmul2_rn(slope2, distance));
+                    float2 x;
+                    if (p.cap_log2 > 0.0f) {  // the cap stands between the scale and the distance bias (uniform for the launch)
+                        const float2 z = __fmul2_rn(make_float2(__uint_as_float(raw[i]), __uint_as_float(raw[i + 1])), cap_scale2);
+                        float2 t;
+                        asm("tanh.approx.f32 %0, %1;" : "=f"(t.x) : "f"(z.x));
+                        asm("tanh.approx.f32 %0, %1;" : "=f"(t.y) : "f"(z.y));
+                        x = __ffma2_rn(t, cap2, __fmul2_rn(slope2, distance));
+                    } else {
+                        x = __ffma2_rn(make_float2(__uint_as_float(raw[i]), __uint_as_float(raw[i + 1])), scale2, __fmul2_rn(slope2, distance));
+                    }
                     distance = __fadd2_rn(distance, make_float2(2.0f, 2.0f));
                     if (masked_tile) {
                         const int key = first_key + i;
@@ -796,7 +808,8 @@ ME_EXPORT int me_attention_tcgen05(const void* map_q, const void* map_k, const v
                                    const int* cu_tokens, const int* context_lens, void* out, float scale, int entries,
                                    int max_new_tokens, int heads, int kv_heads, int head_dim, int page_size,
                                    int table_width, const int* entry_ids, int window, int sink, const float* gate,
-                                   int gate_width, const float* slopes, const float* sink_values, cudaStream_t stream) {
+                                   int gate_width, const float* slopes, const float* sink_values, float softcap,
+                                   cudaStream_t stream) {
     if (entries <= 0) return 0;
     if (window < 0 || (gate != nullptr && gate_width != 1 && gate_width != TC_DIM)) return ME_ERR_ARGUMENT;
     if (head_dim != TC_DIM || kv_heads < 1 || heads % kv_heads) return ME_ERR_UNSUPPORTED;
@@ -806,10 +819,11 @@ ME_EXPORT int me_attention_tcgen05(const void* map_q, const void* map_k, const v
     memcpy(&k, map_k, sizeof(k));
     memcpy(&v, map_v, sizeof(v));
     TcAttnParams p{block_table, cu_tokens, context_lens, entry_ids, static_cast<__nv_bfloat16*>(out), scale * TC_LOG2E,
-                   heads, kv_heads, page_size, table_width, window, (sink || sink_values) ? 1 : 0, gate_width, slopes, sink_values, gate};
+                   heads, kv_heads, page_size, table_width, window, (sink || sink_values) ? 1 : 0, gate_width, slopes, sink_values, gate,
+                   softcap > 0.0f ? softcap * TC_LOG2E : 0.0f};
     const int blocks = (max_new_tokens + TC_ROWS - 1) / TC_ROWS;
     constexpr int SMEM = 6 * TC_HALF_BYTES + 1024 + 256 + 2 * 2 * 128 * 4;
-    if (window > 0 || p.sink || gate != nullptr || slopes != nullptr) {
+    if (window > 0 || p.sink || gate != nullptr || slopes != nullptr || p.cap_log2 > 0.0f) {
         static SharedMemoryOptIn with_options;
         if (const int e = with_options(attention_tcgen05_kernel<true>, SMEM)) return e;
         return launch_kernel(attention_tcgen05_kernel<true>, dim3(heads, blocks, entries), TC_THREADS, SMEM, stream, q, k, v, p);

@@ -526,11 +526,11 @@ def paged_attention(
             raise KernelError("attention over latent rows takes a window and a gate per head, no sink, no distance bias and no cap")
         latent_attention_bf16(q, k_pages, block_table, ctx, out, heads, head_dim, value_dim, scale, window, gate)
         return
-    if v_pages is not None and q.dtype == torch.bfloat16 and value_dim in (None, head_dim) and not softcap:
+    if v_pages is not None and q.dtype == torch.bfloat16 and value_dim in (None, head_dim):
         if attention_bf16.supports(head_dim, heads, kv_heads):
             attention_bf16.paged_attention(
                 q, k_pages, v_pages, block_table, ctx, out, heads, kv_heads, head_dim, scale, window, sink=sink, gate=gate,
-                slopes=slopes, sink_values=sink_values,
+                slopes=slopes, sink_values=sink_values, softcap=softcap,
             )  # fmt: skip
             return
     paged_attention_generic(

@@ -583,6 +583,66 @@ def test_a_far_key_that_stands_out(where, dtype_name):
     assert float((want[0, 0] - v[place, 0]).norm()) < 0.2 * float((want[0, 1] - v[place, 0]).norm())
 
 
+@pytest.mark.parametrize("head_dim", [64, 128])
+@pytest.mark.parametrize("heads,kv_heads,page", [(4, 2, 8), (8, 1, 16), (12, 1, 16), (4, 4, 4)])
+@pytest.mark.parametrize("news", [[1, 1, 1, 1], [90, 5, 130, 2], [1, 40, 1, 7], [400, 90, 130, 300]])
+@pytest.mark.parametrize("cap", [2.0, 20.0])
+def test_tensor_core_attention_with_capped_scores_and_sinks(head_dim, heads, kv_heads, page, news, cap):
+    """The bfloat16 kernels on tensor cores (prompt portions by mma.sync and, for heads of 128, on tcgen05; decode by
+    TMA for groups up to 8 and pages from 8 tokens, else the tiled one; mixed steps) with the cap on the scaled
+    scores and learned sinks, against float64.  Queries and keys are unit vectors times sqrt(head_dim), as behind the
+    unit norm; the scale makes the largest scores pass the smaller cap."""
+    from test_kernels_gpu import fake_context
+
+    from mini_engine_b200.csrc import attention_bf16, ops
+
+    g = torch.Generator().manual_seed(head_dim + heads + page + len(news) + int(cap))
+    lengths = [400, 90, 130, 300]
+    scale = 8.0 / head_dim
+    total_pages = sum(-(-n // page) for n in lengths) + 3
+    order = torch.randperm(total_pages, generator=g).tolist()
+    k_pages = torch.randn(total_pages, kv_heads, page, head_dim, generator=g).to(torch.bfloat16)
+    v_pages = torch.randn(total_pages, kv_heads, page, head_dim, generator=g).to(torch.bfloat16)
+    table = torch.full((len(lengths), max(-(-n // page) for n in lengths) + 1), -1, dtype=torch.int32)
+    sink = 2.0 * torch.randn(heads, generator=g)
+    q_rows, want_rows, entry_of, positions = [], [], [], []
+    for b, (n, new) in enumerate(zip(lengths, news)):
+        q = plain.rms_norm(torch.randn(n, heads, head_dim, generator=g), None, 1e-6).to(torch.bfloat16)
+        k = plain.rms_norm(torch.randn(n, kv_heads, head_dim, generator=g), None, 1e-6)
+        k[n // 2] = q[n - 1, ::heads // kv_heads].float()  # one key that the last query meets at the cap
+        k = k.to(torch.bfloat16)
+        v = torch.randn(n, kv_heads, head_dim, generator=g).to(torch.bfloat16)
+        for i in range(-(-n // page)):
+            table[b, i] = order.pop()
+        for position in range(n):
+            k_pages[table[b, position // page], :, position % page] = k[position]
+            v_pages[table[b, position // page], :, position % page] = v[position]
+        want = plain_capped_attention(q.double()[n - new :], k.double(), v.double(), scale, cap, sink.double())
+        q_rows.append(q[n - new :]), want_rows.append(want)
+        entry_of += [b] * new
+        positions += list(range(n - new, n))
+    data = dict(new_counts=news, lengths=lengths, entry_of=torch.tensor(entry_of, dtype=torch.int32).cuda(),
+                positions=torch.tensor(positions, dtype=torch.int32).cuda())  # fmt: skip
+    q_all = torch.cat(q_rows).reshape(-1, heads * head_dim).contiguous().cuda()
+    want = torch.cat(want_rows).reshape(-1, heads * head_dim).float()
+    out = torch.full_like(q_all, float("nan"))
+    assert attention_bf16.supports(head_dim, heads, kv_heads)
+    ops.paged_attention(
+        q=q_all, k_pages=k_pages.cuda(), v_pages=v_pages.cuda(), block_table=table.cuda(), ctx=fake_context(data), out=out,
+        heads=heads, kv_heads=kv_heads, head_dim=head_dim, scale=scale, window=0, sink_values=sink.cuda(), softcap=cap,
+    )  # fmt: skip
+    torch.cuda.synchronize()
+    assert attention_bf16.take_error() == 0
+    error = float((out.float().cpu() - want).abs().max()) / float(want.abs().max())
+    assert error < 2e-2, f"relative error {error:.3g}"
+    if cap == 2.0:  # the cap matters: without it the same kernels give another result
+        ops.paged_attention(
+            q=q_all, k_pages=k_pages.cuda(), v_pages=v_pages.cuda(), block_table=table.cuda(), ctx=fake_context(data), out=out,
+            heads=heads, kv_heads=kv_heads, head_dim=head_dim, scale=scale, window=0, sink_values=sink.cuda(),
+        )  # fmt: skip
+        assert float((out.float().cpu() - want).abs().max()) / float(want.abs().max()) > 5e-2
+
+
 @pytest.mark.parametrize("heads,dim,vdim,dims", [(2, 16, 8, 16), (3, 24, 40, 8), (1, 6, 5, 2), (2, 64, 64, 64), (1, 128, 32, 32)])
 def test_retention_alone_whole_and_token_by_token(heads, dim, vdim, dims):
     """The recurrence with the rotation, the key scale and a decay per head, then unit norm and gate: a whole prompt
