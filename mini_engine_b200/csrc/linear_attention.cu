@@ -104,6 +104,7 @@ struct ScanArgs {
     float* state;            // [slots + 1][heads][dim][vdim]
     float* out;              // [tokens][heads][vdim] float32: o_t before the norm
     int heads, dim, vdim;
+    int max_count = 0;       // > 0: entries with more tokens than this are left to the chunked kernels
 };
 
 constexpr int SCAN_CHUNK = 16;
@@ -136,6 +137,7 @@ __global__ void __launch_bounds__(32) gla_scan_kernel(ScanArgs a) {
     pdl_trigger();
     pdl_wait();
     const int begin = a.cu_tokens[entry], end = a.cu_tokens[entry + 1];
+    if (a.max_count > 0 && end - begin > a.max_count) return;
     float* state = a.state + ((static_cast<size_t>(a.state_slots[entry]) * a.heads + head) * dim) * a.vdim + column;
 
     float s[DIMP];
@@ -327,21 +329,315 @@ __global__ void __launch_bounds__(256) retention_prepare_kernel(RetentionPrepArg
     }
 }
 
+// ---------------------------------------------------- retention over long portions: chunks of 64 tokens
+
+// With one decay per head the recurrence over a chunk of n tokens (S the state in front of it) has a closed form:
+//
+//   o_i   = a^(i + 1) S^T q_i + sum_(j <= i) a^(i - j) (q_i . k_j) v_j
+//   S_new = a^n S + sum_j a^(n - 1 - j) k_j v_j^T
+//
+// so that a long portion runs as three kernels whose blocks work side by side instead of one warp walking the
+// tokens: (1) every chunk's own sum of decayed k v^T; (2) per (request, head) the states in front of the chunks, one
+// after the other, and the request's new state; (3) every chunk's outputs.  All of it is float32 on the CUDA cores
+// with register tiles of 4 x 4 sums; a sum's order is fixed by the chunk's place in its portion, so a token's
+// bits depend on how its request was cut into steps, by rounding only.  Entries with fewer than `min_count` tokens
+// are left to the walking kernel above.
+constexpr int RC = 64;
+constexpr int STATE_ROWS = 32;   // rows of the state in front of a chunk that are staged at a time
+constexpr int CHUNK_TILES = 4;   // 4 x 4 output tiles of a thread of the output kernel: vdim <= 256
+
+struct ChunkArgs {
+    const float* proj;  // [splits][tokens][width]: the value columns are read from here
+    int splits;
+    size_t split_stride;
+    int width;
+    int v_col;
+    const float* prepared;  // [tokens][heads][3][dim]: rotated q, rotated and scaled k (the third part is not read)
+    const float* decay;     // [heads]
+    const int* cu_tokens;
+    const int* state_slots;
+    const int* fresh;
+    float* state;        // [slots + 1][heads][dim][vdim]
+    float* out;          // [tokens][heads][vdim]
+    float* chunk_state;  // [chunks][heads][dim][vdim]: first every chunk's own sum, then the state in front of it
+    int entries, heads, dim, vdim, min_count;
+};
+
+// The entry that chunk number `chunk` belongs to (entries of at least min_count tokens, cut in order).
+__device__ __forceinline__ bool locate_chunk(const ChunkArgs& a, int chunk, int& entry, int& first_token, int& count) {
+    int seen = 0;
+    for (int b = 0; b < a.entries; ++b) {
+        const int begin = a.cu_tokens[b], n = a.cu_tokens[b + 1] - begin;
+        if (n < a.min_count) continue;
+        const int chunks = (n + RC - 1) / RC;
+        if (chunk < seen + chunks) {
+            const int local = chunk - seen;
+            entry = b, first_token = begin + local * RC, count = min(RC, n - local * RC);
+            return true;
+        }
+        seen += chunks;
+    }
+    return false;
+}
+
+__device__ __forceinline__ float value_sum(const ChunkArgs& a, int token, int head, int e) {
+    const float* src = a.proj + static_cast<size_t>(token) * a.width + a.v_col + head * a.vdim + e;
+    float v = 0.0f;
+    for (int p = 0; p < a.splits; ++p) v += src[p * a.split_stride];
+    return v;
+}
+
+// (1) chunk_state[chunk][head] = sum_j a^(n - 1 - j) k_j v_j^T.  One block per (chunk, head).
+__global__ void __launch_bounds__(256) retention_chunk_state_kernel(ChunkArgs a) {
+    extern __shared__ __align__(16) float chunk_smem[];
+    const int dim = a.dim, vdim = a.vdim, kd = dim + 4, vd = vdim + 4;
+    float* kw = chunk_smem;           // [RC][dim + 4] keys times their decay up to the chunk's end
+    float* v = kw + RC * kd;          // [RC][vdim + 4]
+    __shared__ float pw[RC + 1];
+    const int chunk = blockIdx.x, head = blockIdx.y;
+    pdl_trigger();
+    pdl_wait();
+    int entry, first, count;
+    if (!locate_chunk(a, chunk, entry, first, count)) return;
+    const float decay = a.decay[head];
+    for (int n = threadIdx.x; n <= RC; n += 256) pw[n] = powf(decay, static_cast<float>(n));
+    __syncthreads();
+    for (int i = threadIdx.x; i < count * dim; i += 256) {
+        const int j = i / dim, d = i % dim;
+        kw[j * kd + d] = a.prepared[((static_cast<size_t>(first + j) * a.heads + head) * 3 + 1) * dim + d] * pw[count - 1 - j];
+    }
+    for (int i = threadIdx.x; i < count * vdim; i += 256) {
+        const int j = i / vdim, e = i % vdim;
+        v[j * vd + e] = value_sum(a, first + j, head, e);
+    }
+    __syncthreads();
+    const int across = vdim / 4, tiles = (dim / 4) * across;
+    float* dst = a.chunk_state + (static_cast<size_t>(chunk) * a.heads + head) * dim * vdim;
+    for (int t = threadIdx.x; t < tiles; t += 256) {
+        const int dt = t / across, et = t % across;
+        float acc[4][4] = {};
+        for (int j = 0; j < count; ++j) {
+            const float4 k4 = *reinterpret_cast<const float4*>(kw + j * kd + 4 * dt);
+            const float4 v4 = *reinterpret_cast<const float4*>(v + j * vd + 4 * et);
+            const float kk[4] = {k4.x, k4.y, k4.z, k4.w}, vv[4] = {v4.x, v4.y, v4.z, v4.w};
+#pragma unroll
+            for (int r = 0; r < 4; ++r)
+#pragma unroll
+                for (int c = 0; c < 4; ++c) acc[r][c] = fmaf(kk[r], vv[c], acc[r][c]);
+        }
+#pragma unroll
+        for (int r = 0; r < 4; ++r)
+            *reinterpret_cast<float4*>(dst + static_cast<size_t>(4 * dt + r) * vdim + 4 * et) = make_float4(acc[r][0], acc[r][1], acc[r][2], acc[r][3]);
+    }
+}
+
+// (2) Per (entry, head, four state elements): S walks the entry's chunks; chunk_state[c] becomes the state in front of
+// chunk c, and the request's slot gets the state behind the last one.
+__global__ void __launch_bounds__(256) retention_chunk_prefix_kernel(ChunkArgs a) {
+    const int entry = blockIdx.x, head = blockIdx.y;
+    const int quad = blockIdx.z * 256 + threadIdx.x;
+    pdl_trigger();
+    pdl_wait();
+    const int per_head = a.dim * a.vdim;
+    if (quad * 4 >= per_head) return;
+    const int begin = a.cu_tokens[entry], n = a.cu_tokens[entry + 1] - begin;
+    if (n < a.min_count) return;
+    int first_chunk = 0;
+    for (int b = 0; b < entry; ++b) {
+        const int m = a.cu_tokens[b + 1] - a.cu_tokens[b];
+        if (m >= a.min_count) first_chunk += (m + RC - 1) / RC;
+    }
+    const float decay = a.decay[head];
+    float* slot = a.state + (static_cast<size_t>(a.state_slots[entry]) * a.heads + head) * per_head + quad * 4;
+    float4 s = a.fresh[entry] ? make_float4(0.0f, 0.0f, 0.0f, 0.0f) : *reinterpret_cast<const float4*>(slot);
+    const int chunks = (n + RC - 1) / RC;
+    const float whole = powf(decay, static_cast<float>(RC));
+    for (int c = 0; c < chunks; ++c) {
+        float* own = a.chunk_state + (static_cast<size_t>(first_chunk + c) * a.heads + head) * per_head + quad * 4;
+        const float4 sum = *reinterpret_cast<const float4*>(own);
+        *reinterpret_cast<float4*>(own) = s;
+        const int count = min(RC, n - c * RC);
+        const float p = count == RC ? whole : powf(decay, static_cast<float>(count));
+        s = make_float4(fmaf(p, s.x, sum.x), fmaf(p, s.y, sum.y), fmaf(p, s.z, sum.z), fmaf(p, s.w, sum.w));
+    }
+    *reinterpret_cast<float4*>(slot) = s;
+}
+
+// (3) o_i = a^(i + 1) S^T q_i + sum_(j <= i) a^(i - j) (q_i . k_j) v_j with S = chunk_state[chunk][head].  One block per
+// (chunk, head); thread (it, jt) owns rows it, it + 16, it + 32, it + 48 of a 4 x 4 tile, so that the 16-byte reads of
+// eight neighbouring threads fall into different banks.
+__global__ void __launch_bounds__(256) retention_chunk_output_kernel(ChunkArgs a) {
+    extern __shared__ __align__(16) float chunk_smem[];
+    const int dim = a.dim, vdim = a.vdim, kd = dim + 4, vd = vdim + 4;
+    constexpr int AD = RC + 1;
+    float* q = chunk_smem;        // [RC][dim + 4]
+    float* k = q + RC * kd;       // [RC][dim + 4]
+    float* v = k + RC * kd;       // [RC][vdim + 4]
+    float* w = v + RC * vd;       // [RC][RC + 1]: a^(i - j) (q_i . k_j) for j <= i, else 0
+    float* staged_state = w + RC * AD;  // [STATE_ROWS][vdim + 4]; every part before it holds a multiple of four floats
+    __shared__ float pw[RC + 1];
+    const int chunk = blockIdx.x, head = blockIdx.y;
+    pdl_trigger();
+    pdl_wait();
+    int entry, first, count;
+    if (!locate_chunk(a, chunk, entry, first, count)) return;
+    const float decay = a.decay[head];
+    for (int n = threadIdx.x; n <= RC; n += 256) pw[n] = powf(decay, static_cast<float>(n));
+    for (int i = threadIdx.x; i < RC * dim; i += 256) {
+        const int j = i / dim, d = i % dim;
+        const float* src = a.prepared + ((static_cast<size_t>(first + j) * a.heads + head) * 3) * dim + d;
+        q[j * kd + d] = j < count ? src[0] : 0.0f;
+        k[j * kd + d] = j < count ? src[dim] : 0.0f;
+    }
+    for (int i = threadIdx.x; i < RC * vdim; i += 256) {
+        const int j = i / vdim, e = i % vdim;
+        v[j * vd + e] = j < count ? value_sum(a, first + j, head, e) : 0.0f;
+    }
+    __syncthreads();
+    {
+        const int it = threadIdx.x >> 4, jt = threadIdx.x & 15;
+        float acc[4][4] = {};
+        for (int d = 0; d < dim; d += 4) {
+            float4 q4[4], k4[4];
+#pragma unroll
+            for (int m = 0; m < 4; ++m) {
+                q4[m] = *reinterpret_cast<const float4*>(q + (it + 16 * m) * kd + d);
+                k4[m] = *reinterpret_cast<const float4*>(k + (jt + 16 * m) * kd + d);
+            }
+#pragma unroll
+            for (int m = 0; m < 4; ++m)
+#pragma unroll
+                for (int n = 0; n < 4; ++n) {
+                    acc[m][n] = fmaf(q4[m].x, k4[n].x, acc[m][n]);
+                    acc[m][n] = fmaf(q4[m].y, k4[n].y, acc[m][n]);
+                    acc[m][n] = fmaf(q4[m].z, k4[n].z, acc[m][n]);
+                    acc[m][n] = fmaf(q4[m].w, k4[n].w, acc[m][n]);
+                }
+        }
+#pragma unroll
+        for (int m = 0; m < 4; ++m)
+#pragma unroll
+            for (int n = 0; n < 4; ++n) {
+                const int i = it + 16 * m, j = jt + 16 * n;
+                w[i * AD + j] = j <= i ? acc[m][n] * pw[i - j] : 0.0f;
+            }
+    }
+    __syncthreads();
+    // The state in front of the chunk comes through shared memory, STATE_ROWS rows at a time; a thread keeps the sums
+    // of all its tiles (tiles t, t + 256, ...: at most CHUNK_TILES) over the passes.
+    const int tiles = 16 * (vdim / 4);
+    const float* front = a.chunk_state + (static_cast<size_t>(chunk) * a.heads + head) * dim * vdim;
+    float acc[CHUNK_TILES][4][4] = {};
+    for (int d0 = 0; d0 < dim; d0 += STATE_ROWS) {
+        const int rows = min(STATE_ROWS, dim - d0), across = vdim / 4;
+        for (int i = threadIdx.x; i < rows * across; i += 256) {
+            const int r = i / across, c = i % across;
+            *reinterpret_cast<float4*>(staged_state + r * vd + 4 * c) =
+                __ldg(reinterpret_cast<const float4*>(front + static_cast<size_t>(d0 + r) * vdim + 4 * c));
+        }
+        __syncthreads();
+#pragma unroll
+        for (int u = 0; u < CHUNK_TILES; ++u) {
+            const int t = threadIdx.x + 256 * u;
+            if (t >= tiles) continue;
+            const int it = t & 15, et = t >> 4;
+            for (int d = 0; d < rows; d += 4) {
+                float4 q4[4], s4[4];
+#pragma unroll
+                for (int m = 0; m < 4; ++m) {
+                    q4[m] = *reinterpret_cast<const float4*>(q + (it + 16 * m) * kd + d0 + d);
+                    s4[m] = *reinterpret_cast<const float4*>(staged_state + (d + m) * vd + 4 * et);
+                }
+#pragma unroll
+                for (int m = 0; m < 4; ++m) {
+                    const float qq[4] = {q4[m].x, q4[m].y, q4[m].z, q4[m].w};
+#pragma unroll
+                    for (int r = 0; r < 4; ++r) {
+                        acc[u][m][0] = fmaf(qq[r], s4[r].x, acc[u][m][0]);
+                        acc[u][m][1] = fmaf(qq[r], s4[r].y, acc[u][m][1]);
+                        acc[u][m][2] = fmaf(qq[r], s4[r].z, acc[u][m][2]);
+                        acc[u][m][3] = fmaf(qq[r], s4[r].w, acc[u][m][3]);
+                    }
+                }
+            }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int u = 0; u < CHUNK_TILES; ++u) {
+        const int t = threadIdx.x + 256 * u;
+        if (t >= tiles) continue;
+        const int it = t & 15, et = t >> 4;
+#pragma unroll
+        for (int m = 0; m < 4; ++m) {
+            const float p = pw[it + 16 * m + 1];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) acc[u][m][c] *= p;
+        }
+        for (int j = 0; j < count; ++j) {  // the chunk's own tokens
+            const float4 v4 = *reinterpret_cast<const float4*>(v + j * vd + 4 * et);
+#pragma unroll
+            for (int m = 0; m < 4; ++m) {
+                const float weight = w[(it + 16 * m) * AD + j];
+                acc[u][m][0] = fmaf(weight, v4.x, acc[u][m][0]);
+                acc[u][m][1] = fmaf(weight, v4.y, acc[u][m][1]);
+                acc[u][m][2] = fmaf(weight, v4.z, acc[u][m][2]);
+                acc[u][m][3] = fmaf(weight, v4.w, acc[u][m][3]);
+            }
+        }
+#pragma unroll
+        for (int m = 0; m < 4; ++m) {
+            const int i = it + 16 * m;
+            if (i < count)
+                *reinterpret_cast<float4*>(a.out + (static_cast<size_t>(first + i) * a.heads + head) * vdim + 4 * et) =
+                    make_float4(acc[u][m][0], acc[u][m][1], acc[u][m][2], acc[u][m][3]);
+        }
+    }
+}
+
+static size_t chunk_output_smem(int dim, int vdim) {
+    return (static_cast<size_t>(RC) * (2 * (dim + 4) + (vdim + 4)) + static_cast<size_t>(RC) * (RC + 1) +
+            static_cast<size_t>(STATE_ROWS) * (vdim + 4)) * sizeof(float);
+}
+
+// Whether the chunked kernels take these head sizes (else every entry walks token by token).
+ME_EXPORT int me_retention_chunked_supports(int dim, int vdim) {
+    return dim >= 4 && vdim >= 4 && dim % 4 == 0 && vdim % 4 == 0 && vdim <= 64 * CHUNK_TILES &&
+           chunk_output_smem(dim, vdim) <= 200 * 1024;
+}
+
+// `chunk_min`: entries of at least this many tokens run in chunks (0: none do), with `chunk_state` as scratch of
+// `max_chunks * heads * dim * vdim` floats, max_chunks >= sum over those entries of ceil(tokens / 64).
 ME_EXPORT int me_retention_scan(const float* proj, int splits, long long split_stride, int width, int q_col, int k_col,
                                 int v_col, const float* cos_sin, int rotary_dim, const float* decay, float k_scale,
                                 const int* cu_tokens, const int* state_slots, const int* fresh, float* state, float* out,
-                                float* prepared, int tokens, int entries, int heads, int dim, int vdim,
-                                cudaStream_t stream) {
+                                float* prepared, int tokens, int entries, int heads, int dim, int vdim, int chunk_min,
+                                float* chunk_state, int max_chunks, cudaStream_t stream) {
     if (entries <= 0 || tokens <= 0) return 0;
     if (dim < 1 || vdim < 1 || heads < 1 || rotary_dim < 0 || rotary_dim > dim || rotary_dim % 2) return ME_ERR_ARGUMENT;
     RetentionPrepArgs p{proj, splits, static_cast<size_t>(split_stride), width, q_col, k_col,
                         reinterpret_cast<const float2*>(cos_sin), decay, prepared, k_scale, tokens, heads, dim, rotary_dim};
     const size_t total = static_cast<size_t>(tokens) * heads * dim;
     const int blocks = static_cast<int>(std::min<size_t>((total + 255) / 256, 148 * 16));
-    const int code = launch_kernel(retention_prepare_kernel, blocks, 256, 0, stream, p);
+    int code = launch_kernel(retention_prepare_kernel, blocks, 256, 0, stream, p);
     if (code) return code;
+    if (chunk_min > 0) {
+        if (!me_retention_chunked_supports(dim, vdim) || chunk_state == nullptr || max_chunks < 1) return ME_ERR_ARGUMENT;
+        ChunkArgs c{proj, splits, static_cast<size_t>(split_stride), width, v_col, prepared, decay, cu_tokens, state_slots,
+                    fresh, state, out, chunk_state, entries, heads, dim, vdim, chunk_min};
+        static SharedMemoryOptIn state_opt_in, output_opt_in;
+        const size_t state_smem = static_cast<size_t>(RC) * ((dim + 4) + (vdim + 4)) * sizeof(float);
+        const size_t output_smem = chunk_output_smem(dim, vdim);
+        // The opt-in is remembered per device, so it is made for the largest size that is ever accepted.
+        if ((code = state_opt_in(retention_chunk_state_kernel, 200 * 1024))) return code;
+        if ((code = output_opt_in(retention_chunk_output_kernel, 200 * 1024))) return code;
+        if ((code = launch_kernel_in_order(retention_chunk_state_kernel, dim3(max_chunks, heads), 256, state_smem, stream, c))) return code;
+        const dim3 prefix_grid(entries, heads, (dim * vdim / 4 + 255) / 256);
+        if ((code = launch_kernel_in_order(retention_chunk_prefix_kernel, prefix_grid, 256, 0, stream, c))) return code;
+        if ((code = launch_kernel_in_order(retention_chunk_output_kernel, dim3(max_chunks, heads), 256, output_smem, stream, c))) return code;
+    }
     ScanArgs a{proj, splits, static_cast<size_t>(split_stride), width, v_col, prepared, cu_tokens, state_slots,
-               fresh, state, out, heads, dim, vdim};
+               fresh, state, out, heads, dim, vdim, chunk_min > 0 ? chunk_min - 1 : 0};
     if (dim <= 16) return launch_scan<16>(a, entries, stream);
     if (dim <= 32) return launch_scan<32>(a, entries, stream);
     if (dim <= 64) return launch_scan<64>(a, entries, stream);

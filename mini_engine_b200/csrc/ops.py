@@ -867,16 +867,36 @@ def gla_finish(
     _check(code, "gla_finish")
 
 
+RETENTION_CHUNK = 64  # tokens of a chunk of the chunked retention kernels
+
+
+def retention_chunked_supports(dim: int, vdim: int) -> bool:
+    """Whether the chunked kernels take these head sizes (multiples of four that fit a block's shared memory)."""
+    fn = load_library("linear_attention").me_retention_chunked_supports
+    fn.argtypes, fn.restype = [c_int, c_int], c_int
+    return bool(fn(int(dim), int(vdim)))
+
+
 def retention_scan(
     *, proj: torch.Tensor, columns: dict[str, int], cos_sin: torch.Tensor | None, decay: torch.Tensor, k_scale: float, ctx,
     state: torch.Tensor, out: torch.Tensor, prepared: torch.Tensor, heads: int, dim: int, vdim: int,
+    chunk_min: int = 0, chunk_state: torch.Tensor | None = None,
 ) -> None:  # fmt: skip
     """The recurrence ``S_t = decay_h S_(t-1) + k_t v_t^T``, ``o_t = S_t^T q_t`` over the batch's tokens, entry by entry,
     from and into each request's state slot.  ``proj`` is ``[S, T, width]`` float32 partial sums whose ``columns`` ``q, k,
     v`` say where each projection starts; q and k are rotated by ``cos_sin [T, rotary_dim / 2, 2]`` (their first
     ``rotary_dim`` elements per head, rotate-half) and k is multiplied by ``k_scale``; ``decay`` is float32 ``[heads]``;
-    ``out`` is float32 ``[T, heads, vdim]``; ``prepared`` is float32 scratch of ``T * heads * 3 * dim`` values."""
+    ``out`` is float32 ``[T, heads, vdim]``; ``prepared`` is float32 scratch of ``T * heads * 3 * dim`` values.
+    ``chunk_min`` > 0: entries of at least that many tokens run in chunks of ``RETENTION_CHUNK`` tokens whose blocks work
+    side by side (the closed form of the recurrence over a chunk), with ``chunk_state [chunks, heads, dim, vdim]`` float32 as
+    scratch for at least ``sum ceil(tokens / RETENTION_CHUNK)`` chunks; the other entries walk token by token."""
     _need(proj, torch.float32, "proj"), _need(decay, torch.float32, "decay"), _need(state, torch.float32, "state")
+    max_chunks = 0
+    if chunk_min:
+        _need(chunk_state, torch.float32, "chunk_state")
+        if chunk_state.dim() != 4 or chunk_state.shape[1:] != (heads, dim, vdim) or not retention_chunked_supports(dim, vdim):
+            raise KernelError("retention_scan: the chunks' scratch is [chunks, heads, dim, vdim], and the head sizes must be ones the chunked kernels take")
+        max_chunks = chunk_state.shape[0]
     _need(out, torch.float32, "out"), _need(prepared, torch.float32, "prepared")
     tokens = proj.shape[1]
     if decay.shape != (heads,) or state.shape[1:] != (heads, dim, vdim):
@@ -892,12 +912,14 @@ def retention_scan(
     fn = _fn(
         "linear_attention",
         "me_retention_scan",
-        [c_void_p, c_int, c_longlong] + [c_int] * 4 + [c_void_p, c_int, c_void_p, c_float] + [c_void_p] * 6 + [c_int] * 5 + [c_void_p],
+        [c_void_p, c_int, c_longlong] + [c_int] * 4 + [c_void_p, c_int, c_void_p, c_float] + [c_void_p] * 6 + [c_int] * 6
+        + [c_void_p, c_int, c_void_p],
     )
     code = fn(
         _ptr(proj), proj.shape[0], proj.stride(0), proj.shape[2], columns["q"], columns["k"], columns["v"], _ptr(cos_sin),
         rotary_dim, _ptr(decay), float(k_scale), _ptr(ctx.cu_tokens), _ptr(ctx.state_slots), _ptr(ctx.fresh), _ptr(state),
-        _ptr(out), _ptr(prepared), tokens, ctx.num_entries, heads, dim, vdim, _stream(),
+        _ptr(out), _ptr(prepared), tokens, ctx.num_entries, heads, dim, vdim, int(chunk_min), _ptr(chunk_state), max_chunks,
+        _stream(),
     )  # fmt: skip
     _check(code, "retention_scan")
 

@@ -20,7 +20,10 @@ decays of all tokens for the scan.
 S_(t-1) + k_t v_t^T``: q and k are rotated by position (rotate-half, on their first ``rotary_dim`` elements), k is
 multiplied by ``dim^-1/2`` after its rotation, there are no biases and no decay projection; each head's ``o_t`` is divided
 by its root mean square (no weight), multiplied by ``silu(W_g h_t)`` and projected.  It shares the scan and the finishing
-kernel with the gated form; a kernel of its own rotates, scales and lays q, k and the decays out for the scan.
+kernel with the gated form; a kernel of its own rotates, scales and lays q, k and the decays out for the scan.  Portions
+of more than ``CHUNKED_MIN_TOKENS`` tokens do not walk token by token: a constant decay gives the recurrence over a chunk
+of 64 tokens a closed form (the state in front of the chunk, decayed, plus a causal product inside the chunk), which
+three kernels compute with all chunks side by side, in float32.
 """
 
 from __future__ import annotations
@@ -120,6 +123,11 @@ class GatedLinearAttention(Mixer):
         return self.out.forward(gated, ctx, "gla.o")
 
 
+# An entry of at least this many tokens runs in chunks.  Below, the walk is as fast, and decoded tokens and short
+# portions keep the bits of a token-by-token run.
+CHUNKED_MIN_TOKENS = 33
+
+
 @register("mixer", "retention")
 class Retention(Mixer):
     capturable = True
@@ -161,6 +169,7 @@ class Retention(Mixer):
         self.proj: Linear | None = None
         self.out: Linear | None = None
         self.decay: torch.Tensor | None = None
+        self.chunked: bool | None = None  # whether the chunked kernels take the head sizes: asked once, on the device
 
     def state(self) -> StateSpec:
         return StateSpec((self.heads, self.dim, self.vdim), torch.float32)
@@ -193,9 +202,17 @@ class Retention(Mixer):
         proj = self.proj.forward(h, ctx, "retention.proj")
         raw = ctx.buffer("retention.raw", (tokens, self.heads * self.vdim), torch.float32)
         prepared = ctx.buffer("retention.prepared", (tokens, self.heads * 3 * self.dim), torch.float32)
+        if self.chunked is None:
+            self.chunked = ops.retention_chunked_supports(self.dim, self.vdim)
+        chunk_min, chunk_state = 0, None
+        if self.chunked and ctx.max_query_len >= CHUNKED_MIN_TOKENS:  # a step's longest entry is known on the host
+            chunks = tokens // ops.RETENTION_CHUNK + ctx.num_entries
+            chunk_min = CHUNKED_MIN_TOKENS
+            chunk_state = ctx.workspace.growing("retention.chunks", (chunks, self.heads, self.dim, self.vdim), torch.float32)
         ops.retention_scan(
             proj=proj, columns=self.columns, cos_sin=table, decay=self.decay, k_scale=self.k_scale, ctx=ctx,
             state=cache.state, out=raw, prepared=prepared, heads=self.heads, dim=self.dim, vdim=self.vdim,
+            chunk_min=chunk_min, chunk_state=chunk_state,
         )  # fmt: skip
         gated = ctx.buffer("retention.out", (tokens, self.heads * self.vdim), ctx.dtype)
         ops.gla_finish(
