@@ -452,13 +452,23 @@ __global__ void __launch_bounds__(256) retention_chunk_prefix_kernel(ChunkArgs a
     float4 s = a.fresh[entry] ? make_float4(0.0f, 0.0f, 0.0f, 0.0f) : *reinterpret_cast<const float4*>(slot);
     const int chunks = (n + RC - 1) / RC;
     const float whole = powf(decay, static_cast<float>(RC));
-    for (int c = 0; c < chunks; ++c) {
-        float* own = a.chunk_state + (static_cast<size_t>(first_chunk + c) * a.heads + head) * per_head + quad * 4;
-        const float4 sum = *reinterpret_cast<const float4*>(own);
-        *reinterpret_cast<float4*>(own) = s;
-        const int count = min(RC, n - c * RC);
-        const float p = count == RC ? whole : powf(decay, static_cast<float>(count));
-        s = make_float4(fmaf(p, s.x, sum.x), fmaf(p, s.y, sum.y), fmaf(p, s.z, sum.z), fmaf(p, s.w, sum.w));
+    const size_t step = static_cast<size_t>(a.heads) * per_head;  // floats between two chunks of this head
+    float* own = a.chunk_state + (static_cast<size_t>(first_chunk) * a.heads + head) * per_head + quad * 4;
+    constexpr int AHEAD = 8;  // chunks whose sums are fetched together: the walk waits for memory once per AHEAD chunks
+    for (int c0 = 0; c0 < chunks; c0 += AHEAD) {
+        float4 sum[AHEAD];
+#pragma unroll
+        for (int i = 0; i < AHEAD; ++i)
+            if (c0 + i < chunks) sum[i] = *reinterpret_cast<const float4*>(own + (c0 + i) * step);
+#pragma unroll
+        for (int i = 0; i < AHEAD; ++i) {
+            const int c = c0 + i;
+            if (c >= chunks) break;
+            *reinterpret_cast<float4*>(own + c * step) = s;
+            const int count = min(RC, n - c * RC);
+            const float p = count == RC ? whole : powf(decay, static_cast<float>(count));
+            s = make_float4(fmaf(p, s.x, sum[i].x), fmaf(p, s.y, sum[i].y), fmaf(p, s.z, sum[i].z), fmaf(p, s.w, sum[i].w));
+        }
     }
     *reinterpret_cast<float4*>(slot) = s;
 }
@@ -466,14 +476,14 @@ __global__ void __launch_bounds__(256) retention_chunk_prefix_kernel(ChunkArgs a
 // (3) o_i = a^(i + 1) S^T q_i + sum_(j <= i) a^(i - j) (q_i . k_j) v_j with S = chunk_state[chunk][head].  One block per
 // (chunk, head); thread (it, jt) owns rows it, it + 16, it + 32, it + 48 of a 4 x 4 tile, so that the 16-byte reads of
 // eight neighbouring threads fall into different banks.
-__global__ void __launch_bounds__(256) retention_chunk_output_kernel(ChunkArgs a) {
+__global__ void __launch_bounds__(256, 2) retention_chunk_output_kernel(ChunkArgs a) {
     extern __shared__ __align__(16) float chunk_smem[];
     const int dim = a.dim, vdim = a.vdim, kd = dim + 4, vd = vdim + 4;
     constexpr int AD = RC + 1;
     float* q = chunk_smem;        // [RC][dim + 4]
-    float* k = q + RC * kd;       // [RC][dim + 4]
-    float* v = k + RC * kd;       // [RC][vdim + 4]
-    float* w = v + RC * vd;       // [RC][RC + 1]: a^(i - j) (q_i . k_j) for j <= i, else 0
+    float* k = q + RC * kd;       // [RC][dim + 4] while the weights are formed; then the values take its place:
+    float* v = k;                 // [RC][vdim + 4]
+    float* w = k + RC * max(kd, vd);  // [RC][RC + 1]: a^(i - j) (q_i . k_j) for j <= i, else 0
     float* staged_state = w + RC * AD;  // [STATE_ROWS][vdim + 4]; every part before it holds a multiple of four floats
     __shared__ float pw[RC + 1];
     const int chunk = blockIdx.x, head = blockIdx.y;
@@ -488,10 +498,6 @@ __global__ void __launch_bounds__(256) retention_chunk_output_kernel(ChunkArgs a
         const float* src = a.prepared + ((static_cast<size_t>(first + j) * a.heads + head) * 3) * dim + d;
         q[j * kd + d] = j < count ? src[0] : 0.0f;
         k[j * kd + d] = j < count ? src[dim] : 0.0f;
-    }
-    for (int i = threadIdx.x; i < RC * vdim; i += 256) {
-        const int j = i / vdim, e = i % vdim;
-        v[j * vd + e] = j < count ? value_sum(a, first + j, head, e) : 0.0f;
     }
     __syncthreads();
     {
@@ -523,6 +529,10 @@ __global__ void __launch_bounds__(256) retention_chunk_output_kernel(ChunkArgs a
             }
     }
     __syncthreads();
+    for (int i = threadIdx.x; i < RC * vdim; i += 256) {  // the keys are done with: the values take their place
+        const int j = i / vdim, e = i % vdim;
+        v[j * vd + e] = j < count ? value_sum(a, first + j, head, e) : 0.0f;
+    }
     // The state in front of the chunk comes through shared memory, STATE_ROWS rows at a time; a thread keeps the sums
     // of all its tiles (tiles t, t + 256, ...: at most CHUNK_TILES) over the passes.
     const int tiles = 16 * (vdim / 4);
@@ -596,7 +606,7 @@ __global__ void __launch_bounds__(256) retention_chunk_output_kernel(ChunkArgs a
 }
 
 static size_t chunk_output_smem(int dim, int vdim) {
-    return (static_cast<size_t>(RC) * (2 * (dim + 4) + (vdim + 4)) + static_cast<size_t>(RC) * (RC + 1) +
+    return (static_cast<size_t>(RC) * ((dim + 4) + std::max(dim + 4, vdim + 4)) + static_cast<size_t>(RC) * (RC + 1) +
             static_cast<size_t>(STATE_ROWS) * (vdim + 4)) * sizeof(float);
 }
 
