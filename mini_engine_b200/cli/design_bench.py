@@ -25,7 +25,7 @@ attention has as many heads with 128 plain and 64 rotated query/key elements, va
 and a query latent of three eighths of the width, and the same window; its feed-forward is as wide as Qwen3's.
 
 Bizurax gets four layers in the order attention, retention, latent attention, retention, on four residual streams; its
-attention has Qwen3's head counts and head size, no window, scores capped at 20 and a learned sink; its retention has as
+attention has Qwen3's head counts and head size, no window, scores capped at 30 and a learned sink; its retention has as
 many heads with the key and value widths of Pimezen's linear attention; its latent attention has 128 plain and 64 rotated
 query/key elements, values of 128 and a latent of 512; the attention layers have a squared-relu feed-forward one and a
 half times as wide as Qwen3's (the same weights), the retention layers 8 routed units a quarter as wide of which a token
@@ -97,10 +97,10 @@ def bizurax_config(size: dict):
     from mini_engine_b200.config import BizuraxConfig
 
     d, h, ff = size["head_dim"], size["heads"], size["ff"]
-    attention = {"heads": h, "kv_heads": size["kv_heads"], "dim": d, "vdim": d, "scale": 10.0 / d, "softcap": 20.0,
-                 "rot": {"base": 250000.0, "dims": d, "scaling": {"factor": 4.0}}}  # fmt: skip
+    attention = {"heads": h, "kv_heads": size["kv_heads"], "dim": d, "vdim": d, "scale": 8.0 / d, "softcap": 30.0,
+                 "rot": {"base": 500000.0, "dims": d, "scaling": {"factor": 8.0}}}  # fmt: skip
     retention = {"heads": h, "dim": size["lin_dim"], "vdim": size["lin_vdim"], "decay": [1.0 - 2.0 ** (-5 - 6 * i / h) for i in range(h)],
-                 "rot": {"base": 1e6, "dims": size["lin_dim"]}}  # fmt: skip
+                 "rot": {"base": 2e5, "dims": size["lin_dim"]}}  # fmt: skip
     latent = {"heads": h, "dim": d, "rot_dim": LATENT_ROT, "vdim": d, "kv_rank": LATENT_RANK, "scale": (d + LATENT_ROT) ** -0.5,
               "rot": {"base": 1e4, "dims": LATENT_ROT}}  # fmt: skip
     dense = {"kind": "dense", "ff": 3 * ff // 2}

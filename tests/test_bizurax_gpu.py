@@ -81,9 +81,9 @@ CONFIG_T = {
     "architecture": "Bizurax", "vocab": 64, "width": 64, "norm": {"eps": 1e-6}, "residual_mult": 0.5, "streams": 2,
     "loop": {"start": 0, "stop": 3, "times": 2},
     "layers": [
-        {"type": "attention", "mixer": attention(4, 2, 64, 64, 0.125, 20.0, rot(250000.0, 64, 4.0)), "mlp": dense(64)},
-        {"type": "retention", "mixer": retention(2, 64, 64, [0.984375, 0.9995], rot(1e6, 64)), "mlp": moe(8, 3, 64, 128)},
-        {"type": "latent_attention", "mixer": latent(4, 32, 32, 32, 64, 0.125, 10000.0), "mlp": moe(8, 2, 32, 64)},
+        {"type": "attention", "mixer": attention(4, 2, 64, 64, 0.125, 30.0, rot(500000.0, 64, 8.0)), "mlp": dense(64)},
+        {"type": "retention", "mixer": retention(2, 64, 64, [0.96875, 0.998], rot(2e5, 64)), "mlp": moe(8, 3, 64, 128)},
+        {"type": "latent_attention", "mixer": latent(4, 32, 32, 32, 64, 0.15, 40000.0), "mlp": moe(8, 2, 32, 64)},
     ],
 }  # fmt: skip
 # Sizes that no fast path takes: a width that is no multiple of 8, odd head widths, one head, one stream, one routed
