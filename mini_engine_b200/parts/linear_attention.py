@@ -151,6 +151,8 @@ class Retention(Mixer):
         (default ``head_dim ** -0.5``); ``position_encoding``: a rotate-half rotation that the kernel applies, or none."""
         if min(num_heads, head_dim, value_dim) < 1:
             raise ValueError("retention: sizes must be positive")
+        if head_dim > 192:
+            raise ValueError(f"retention: the walking kernel keeps a state column of at most 192 key channels in registers, got {head_dim}")
         if len(decay) != num_heads or not all(0.0 < float(a) <= 1.0 for a in decay):
             raise ValueError(f"retention: one decay in (0, 1] per head ({num_heads}), got {list(decay)}")
         self.hidden, self.heads, self.dim, self.vdim = hidden_size, num_heads, head_dim, value_dim

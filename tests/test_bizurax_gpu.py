@@ -712,10 +712,14 @@ def test_latent_layer_and_capped_layer_against_plain(tmp_path):
     """One latent layer (neighbour pairs rotated) and one capped attention layer as whole models, far keys included."""
     for layer in (
         {"type": "latent_attention", "mixer": latent(4, 16, 16, 16, 48, 0.2, 10000.0), "mlp": None},
+        # a latent of 128 and rows of 192: the sizes that the tensor-core kernels over latent rows take in bfloat16
+        {"type": "latent_attention", "mixer": latent(4, 64, 64, 32, 128, 0.09, 5000.0), "mlp": None},
+        # heads of 128, keys and values alike: the tensor-core attention kernels with the cap and the sink
+        {"type": "attention", "mixer": attention(2, 1, 128, 128, 0.07, 6.0, rot(10000.0, 64, 2.0)), "mlp": None},
         {"type": "attention", "mixer": attention(4, 2, 32, 16, 0.3, 4.0, rot(10000.0, 16, 2.0)), "mlp": None},
     ):
         raw = {"architecture": "Bizurax", "vocab": 100, "width": 64, "norm": {"eps": 1e-5}, "residual_mult": 1.0, "layers": [layer]}
-        folder = write_model(tmp_path / layer["type"], raw, seed=5, scale=20.0)
+        folder = write_model(tmp_path / f"{layer['type']}_{layer['mixer']['dim']}", raw, seed=5, scale=20.0)
         requests = {"a": random_ids(1, 300, 100), "b": random_ids(2, 2, 100)}
         for dtype_name in ("float32", "bfloat16"):
             for maker in (schedules.whole, schedules.changing_portions, lambda r: schedules.tail_one_by_one(r, 32)):
