@@ -100,12 +100,14 @@ def bizurax_spec(cfg: BizuraxConfig) -> ModelSpec:
         subs = ("mixer",) if layer.mlp is None else ("mixer", "feed_forward")
         if layer.mlp is not None:
             norms["feed_forward_norm"] = PartSpec("rmsnorm", {"name": "norm2", "eps": eps})
+        # a checkpoint may carry the second sublayer's norm and coefficients for a layer that has no feed-forward
+        unused = () if layer.mlp is not None else ("norm2",) if cfg.streams is None else ("norm2", "hc2.in", "hc2.mix", "hc2.out")
         if cfg.streams is None:
-            block, params = "prenorm", {"residual_mult": cfg.residual_mult}
+            block, params = "prenorm", {"residual_mult": cfg.residual_mult, "unused_names": unused}
         else:
             tensors = {"mixer": "hc1", "feed_forward": "hc2"}
             names = {sub: {"read": tensors[sub] + ".in", "mix": tensors[sub] + ".mix", "share": tensors[sub] + ".out"} for sub in subs}
-            block, params = "hyper_prenorm", {"streams": cfg.streams, "names": names, "residual_mult": cfg.residual_mult}
+            block, params = "hyper_prenorm", {"streams": cfg.streams, "names": names, "residual_mult": cfg.residual_mult, "unused_names": unused}
         layers.append(
             LayerSpec(
                 prefix=f"l{index}.", block=block + ("_mixer_only" if layer.mlp is None else ""),

@@ -18,12 +18,17 @@ class PreNormBlock(Block):
 
     capturable = True
 
-    def __init__(self, mixer, feed_forward, norms, *, prefix: str = "", hidden_size: int = 0, residual_mult: float = 1.0):
+    def __init__(self, mixer, feed_forward, norms, *, prefix: str = "", hidden_size: int = 0, residual_mult: float = 1.0, unused_names=()):
         """``residual_mult``: a constant that every sublayer's output is multiplied by before it is added, ``x + m *
-        sublayer(norm(x))`` (1: the plain sum).  A layer may have no feed-forward (``prenorm_mixer_only``)."""
+        sublayer(norm(x))`` (1: the plain sum).  A layer may have no feed-forward (``prenorm_mixer_only``).
+        ``unused_names``: tensors of the layer that a checkpoint may carry although the layer has no use for them."""
         super().__init__(mixer, feed_forward, norms)
         self.residual_mult, self.hidden = float(residual_mult), hidden_size
         self.mult: torch.Tensor | None = None
+        self.unused = [prefix + name for name in unused_names]
+
+    def weight_specs(self) -> list[WeightSpec]:
+        return super().weight_specs() + [WeightSpec(name, (), role="vector", optional=True) for name in self.unused]
 
     def load(self, tensors) -> None:
         super().load(tensors)
@@ -60,9 +65,10 @@ class HyperConnectionBlock(Block):
 
     capturable = True
 
-    def __init__(self, mixer, feed_forward, norms, *, prefix: str, hidden_size: int, streams: int, names, residual_mult: float = 1.0):
+    def __init__(self, mixer, feed_forward, norms, *, prefix: str, hidden_size: int, streams: int, names, residual_mult: float = 1.0, unused_names=()):
         """``names``: for ``"mixer"`` (and ``"feed_forward"``) the tensor names of ``read``, ``mix`` and ``share``
-        behind the layer's prefix."""
+        behind the layer's prefix.  ``unused_names``: tensors of the layer that a checkpoint may carry although the
+        layer has no use for them (the norm and the coefficients of a feed-forward that the layer does not have)."""
         super().__init__(mixer, feed_forward, norms)
         if not 1 <= streams <= 8:
             raise ValueError(f"hyper_prenorm takes 1 to 8 residual streams, got {streams}")
@@ -72,6 +78,7 @@ class HyperConnectionBlock(Block):
         self.count, self.hidden, self.mult = int(streams), hidden_size, float(residual_mult)
         self.names = {sub: {key: prefix + name for key, name in group.items()} for sub, group in names.items()}
         self.coefficients: dict[str, dict[str, torch.Tensor]] = {}
+        self.unused = [prefix + name for name in unused_names]
 
     def weight_specs(self) -> list[WeightSpec]:
         specs = super().weight_specs()
@@ -81,7 +88,7 @@ class HyperConnectionBlock(Block):
                 WeightSpec(group["share"], (self.count,), role="vector", init="ones_normal"),
                 WeightSpec(group["mix"], (self.count, self.count), role="vector", init="eye_normal"),
             ]
-        return specs
+        return specs + [WeightSpec(name, (), role="vector", optional=True) for name in self.unused]
 
     def load(self, tensors) -> None:
         super().load(tensors)

@@ -91,15 +91,33 @@ def test_optional_keys_may_be_absent():
     assert not any(".hc" in s.name for s in declared_weights(spec))
 
 
+def test_a_checkpoint_may_carry_the_tensors_of_a_feed_forward_that_a_layer_does_not_have(tmp_path):
+    from mini_engine_b200.weights.loader import check_specs
+    from mini_engine_b200.weights.safetensors_io import SafetensorsFile, write_safetensors
+
+    cfg = BizuraxConfig.from_dict(raw_config())
+    write_random_model(tmp_path, cfg, seed=1)
+    stored = SafetensorsFile(tmp_path / "model.safetensors")
+    assert "l2.norm2" not in stored.entries
+    tensors = {name: stored.tensor(name).clone() for name in stored.entries}
+    tensors.update({"l2.norm2": torch.ones(48, dtype=torch.bfloat16), "l2.hc2.in": torch.ones(3, dtype=torch.bfloat16),
+                    "l2.hc2.out": torch.ones(3, dtype=torch.bfloat16), "l2.hc2.mix": torch.eye(3, dtype=torch.bfloat16)})  # fmt: skip
+    write_safetensors(tmp_path / "more.safetensors", tensors)
+    specs = declared_weights(architecture_for("Bizurax").build_spec(cfg))
+    check_specs(specs, SafetensorsFile(tmp_path / "more.safetensors").entries)  # nothing is unexpected
+    check_specs(specs, stored.entries)  # and nothing is missing without them
+
+
 def test_declared_tensors():
     spec = architecture_for("Bizurax").build_spec(BizuraxConfig.from_dict(raw_config()))
     declared = {s.name: s for s in declared_weights(spec)}
     assert declared["embed"].shape == (90, 48) and declared["head"].shape == (90, 48) and declared["head"].alias_of is None
-    assert declared["final.norm"].shape == (48,) and declared["l1.norm2"].shape == (48,) and "l2.norm2" not in declared
+    assert declared["final.norm"].shape == (48,) and declared["l1.norm2"].shape == (48,) and not declared["l1.norm2"].optional
     for sub in ("hc1", "hc2"):
         assert declared[f"l0.{sub}.in"].shape == (3,) and declared[f"l0.{sub}.out"].shape == (3,) and declared[f"l0.{sub}.mix"].shape == (3, 3)
         assert declared[f"l0.{sub}.mix"].role == "vector"
-    assert "l2.hc1.in" in declared and "l2.hc2.in" not in declared  # a layer without feed-forward has one set
+    # a layer without feed-forward has one set; a checkpoint may carry the other set and its norm all the same
+    assert "l2.hc1.in" in declared and all(declared[f"l2.{name}"].optional for name in ("norm2", "hc2.in", "hc2.mix", "hc2.out"))
     assert declared["l0.mix.q"].shape == (72, 48) and declared["l0.mix.dkv"].shape == (28, 48) and declared["l0.mix.dkv.norm"].shape == (20,)
     assert declared["l0.mix.uk"].shape == (48, 20) and declared["l0.mix.uv"].shape == (72, 20) and "l0.mix.dq" not in declared
     assert declared["l1.mix.q"].shape == (48, 48) and declared["l1.mix.v"].shape == (72, 48) and declared["l1.mix.g"].shape == (72, 48)
